@@ -1,0 +1,90 @@
+"""The CPU oracle against the reference's own outputs (tests/golden/bfp_golden.npz) and its C twin."""
+import numpy as np
+import pytest
+from oracle import bfp_oracle as o
+
+
+def test_bf16_rounding(golden):
+  assert np.array_equal(o.bf16_bits(golden["bits_in"].view(np.float32)), golden["bf16_bits"])
+  assert np.array_equal(o.round_bf16_bits(golden["round_in"].view(np.float32)).astype(np.uint32), golden["round_bf16"])
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("case", ["spread", "weights", "cache", "corner"])
+def test_bfp_values(golden, fmt, case):
+  a = golden[f"bfp_{case}_in"]
+  assert np.array_equal(o.bfp_values(a, fmt), golden[f"bfp_{case}_{fmt}"])
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_decode(golden, c_oracle, fmt):
+  tiles = golden[f"dec_{fmt}_in"]
+  assert np.array_equal(o.unpack_tiles(tiles, fmt), golden[f"dec_{fmt}"])
+  assert np.array_equal(c_oracle.unpack(tiles, fmt), golden[f"dec_{fmt}"])
+
+
+@pytest.mark.parametrize("name", ["a", "b", "row", "col", "one", "x"])
+def test_tilize(golden, name):
+  a, want = golden[f"tile_{name}_in"], golden[f"tile_{name}"]
+  tiles = o.tilize(a)
+  assert np.array_equal(tiles, want)
+  if a.shape[1] > 1 and a.shape[2] > 1: assert np.array_equal(o.untilize(tiles, *a.shape), a)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("case", ["spread", "weights", "cache", "corner"])
+def test_pack_bytes(golden, c_oracle, fmt, case):
+  # pack to bytes, decode as the unpacker does: the values must be the reference's gpt2.bfp values. Runs whose shared
+  # exponent is below 8 are left out of the value check: there the reference's decoder wraps the exponent while
+  # gpt2.bfp keeps the tiny value, and no reference test pins which the chip does.
+  a = golden[f"bfp_{case}_in"]
+  tiles = o.tilize(o.bf16_bits(a))
+  packed = o.pack_tiles(tiles, fmt)
+  assert np.array_equal(packed, c_oracle.pack(tiles, fmt))
+  dec = o.unpack_tiles(packed, fmt)
+  assert np.array_equal(dec, c_oracle.unpack(packed, fmt))
+  got = o.untilize(o.bf16_floats(dec), 1, *a.shape)[0].astype(np.float64)
+  want = golden[f"bfp_{case}_{fmt}"]
+  top = np.repeat((o.bf16_bits(a) >> 7 & 255).reshape(a.shape[0], -1, 16).max(-1), 16, axis=1)
+  ok = top >= 8
+  assert ok.mean() > 0.9 or case == "corner"
+  assert np.array_equal(got[ok], want[ok])
+  assert not np.isinf(got[ok]).any() or case == "corner"
+
+
+def test_known_answers(c_oracle):
+  # put of [2, 3] into block-float tiles decodes to 0x4000, 0x4040 (test/test_kernels.py:2098-2103); zeros pack to
+  # all-zero bytes (test/test_kernels.py:351-368); -0 packs without a sign, since the unpacker reads -0 as -inf.
+  a = np.zeros((32, 32), np.float32)
+  a[:, 0], a[:, 1] = 2, 3
+  for fmt in ("bfp8", "bfp4"):
+    dec = o.unpack_tiles(o.pack_tiles(o.tilize(o.bf16_bits(a)), fmt), fmt).reshape(4, 16, 16)
+    assert np.all(dec[[0, 2], :, :2] == [0x4000, 0x4040])
+    z = o.pack_tiles(o.tilize(o.bf16_bits(np.zeros((70, 100), np.float32))), fmt)
+    assert not z.any()
+    neg = o.pack_tiles(o.tilize(o.bf16_bits(np.full((32, 32), -0.0, np.float32))), fmt)
+    assert not neg.any()
+    assert np.array_equal(c_oracle.pack(np.full((1, 1024), 0x8000, np.uint16), fmt), neg)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_stream_layout_is_a_permutation(fmt):
+  rng = np.random.default_rng(2)
+  for tr, tc in ((1, 1), (3, 5), (2, 16), (4, 37)):
+    tiles = rng.integers(0, 256, (tr * tc, o.tile_bytes(fmt)), dtype=np.uint16).astype(np.uint8)
+    s = o.to_stream(tiles, fmt, tr, tc)
+    assert s.size == tiles.size and np.array_equal(np.sort(s), np.sort(tiles.reshape(-1)))
+    assert np.array_equal(o.from_stream(s, fmt, tr, tc), tiles)
+
+
+def test_matmul_and_argmax():
+  rng = np.random.default_rng(0)
+  x, w, v = rng.normal(0, 1, (4, 64)), rng.normal(0, 0.02, (64, 96)), rng.normal(0, 0.02, (64, 96))
+  wd, vd = o.dequant(w, "bfp8"), o.dequant(v, "bfp4")
+  assert np.array_equal(wd, o.bfp_values(w, "bfp8").astype(np.float32))
+  y = o.matmul(x, wd, "glu", vd)
+  g = x.astype(np.float32) @ wd
+  assert np.allclose(y, g / (1 + np.exp(-g)) * (x.astype(np.float32) @ vd))
+  assert np.array_equal(o.matmul(x, wd, "relu"), np.maximum(g, 0))
+  assert o.argmax(np.array([[1.0, 3.0, 3.0], [-0.0, 0.0, -1.0]])).tolist() == [1, 0]
+  assert o.rel_err(g, g) == 0
