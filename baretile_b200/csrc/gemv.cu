@@ -1,0 +1,468 @@
+// Decode matmul for up to 32 token rows: out = epilogue(alpha * x @ W + add), W block-float in streaming layout.
+//
+// The kernel is bound by HBM: every packed weight byte is read once, by a bulk (TMA) copy into a ring of
+// shared-memory stages, and dequantised in registers on its way into a bf16 MMA with fp32 accumulators.
+//
+// Decomposition ("stream-K"). The weight matrix is cut into sub-panels of WC tile columns. A unit is one tile
+// row of one sub-panel (WC tiles). Units are numbered sub-panel by sub-panel and dealt out in equal contiguous
+// ranges to one persistent CTA per SM, so every SM streams the same number of bytes whatever the shape. A CTA
+// whose range ends inside a sub-panel writes its fp32 partial sums to scratch; the last CTA to arrive at that
+// sub-panel (an atomic counter tells it) adds the partials in CTA order, so results do not depend on timing,
+// and runs the epilogue.
+//
+// Inside a CTA: warp 16 is the producer. One of its lanes waits for a free stage, announces the stage's bytes
+// to the stage's mbarrier and issues the bulk copies (weights and the matching tiles of x). The 16 consumer
+// warps form a WC x KS grid: warp (ck, cc) takes column cc of the sub-panel and every KS-th tile row of the
+// stage, so x tiles in shared memory serve WC warps. A weight tile is four 16x16 faces; a face is one
+// m16n8k16 MMA with the face's 16 output channels as the MMA's rows, 16 input channels as its K and up to 8
+// tokens as its columns. The 16 weights of a face row share an exponent e: the lane builds bf16 lanes
+// (sign << 15 | magnitude), i.e. +-q * 2^-133 as a bf16 subnormal, and multiplies by 2^(e - 64) as a packed bf16
+// multiply, which gives q * 2^(e - 133) * 2^-64 exactly; the epilogue multiplies the sums by 2^64.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "stream_layout.cuh"
+
+using namespace bt;
+
+namespace {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMaxStages = 8;
+constexpr int kMaxCtas = 256;
+constexpr int kMaxSubPanels = 16384;
+constexpr uint32_t kSpinLimit = 1u << 21;
+constexpr int kSmemBudget = 225 * 1024;
+
+// Scratch layout (byte offsets into the caller's workspace).
+constexpr size_t kWsError = 0;                                   // int: set to nonzero when a wait gave up
+constexpr size_t kWsPanelsDone = 4;                              // int: sub-panels finished (argmax epilogue)
+constexpr size_t kWsCounters = 256;                              // int[kMaxSubPanels]: CTAs arrived at a sub-panel
+constexpr size_t kWsArgVal = kWsCounters + 4 * kMaxSubPanels;    // float[kMaxSubPanels][32]
+constexpr size_t kWsArgIdx = kWsArgVal + 4 * 32 * kMaxSubPanels; // int[kMaxSubPanels][32]
+constexpr size_t kWsPartials = kWsArgIdx + 4 * 32 * kMaxSubPanels;
+constexpr size_t kSlotFloatsMax = 2 * 16 * 2 * 4 * 4 * 32;       // NW * WC * 2 * TG * 4 * 32 at its largest
+constexpr size_t kWsBytes = kWsPartials + (size_t)kMaxCtas * 2 * kSlotFloatsMax * 4;
+
+struct GemvParams {
+  const uint8_t *x;
+  const uint8_t *w[2];
+  const uint16_t *add;
+  void *out;
+  float *arg_val;
+  int *arg_idx;
+  uint8_t *work;
+  float alpha;
+  int arg_base, M, KT, TC, epi, out_fp32, nstages;
+};
+
+template <int FMT, int NW, int TG, int WC>
+struct Config {
+  static constexpr int KS = kConsumerWarps / WC;                 // k-slices: warps sharing a column
+  static constexpr int T = NW == 2 ? 1 : 2;                      // tile rows a warp takes per stage
+  static constexpr int UPS = KS * T;                             // units (tile rows) per stage
+  static constexpr int TB = tile_bytes(FMT);
+  static constexpr int XB = TG == 1 ? 512 : TG == 2 ? 1024 : 2048;  // bytes of an x tile staged: rows 0-7, 0-15 or all 32
+  static constexpr int W_BYTES = UPS * NW * WC * TB;
+  static constexpr int STAGE = (W_BYTES + UPS * XB + 127) / 128 * 128;
+  static constexpr int ACC = NW * 2 * TG * 4;                    // accumulator floats per lane
+  static constexpr int RED = KS > 1 ? WC * ACC * 32 * 4 : 0;     // cross-warp reduction buffer
+  static constexpr int FIXED = 4352 + RED;                       // barriers, flags, argmax staging, reduction buffer
+  static constexpr size_t SLOT = (size_t)WC * ACC * 32;          // floats in one partial slot
+};
+
+__device__ __forceinline__ long long range_start(long long units, int b, int ctas) { return units * b / ctas; }
+__device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
+  int b = (int)(u * ctas / units);
+  while (b + 1 < ctas && range_start(units, b + 1, ctas) <= u) b++;
+  while (b > 0 && range_start(units, b, ctas) > u) b--;
+  return b;
+}
+
+// bf16 lanes 2^(e + 63 - 127) for two exponent bytes of `ew` (bytes 0,1 for HI = 0; bytes 2,3 for HI = 1).
+template <int HI>
+__device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
+  return prmt(ew, 0u, HI ? 0x4342u : 0x4140u) * 128u + 0x1F801F80u;
+}
+
+// One weight tile times the staged x tile, added into acc[ng][tg][4].
+template <int FMT, int TG>
+__device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t xs, int lane, float (&acc)[2][TG][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint4 ev = lds128(tile + t * 16);
+  const uint32_t ee[4] = {ev.x, ev.y, ev.z, ev.w};
+  uint4 wq = make_uint4(0, 0, 0, 0);
+  if (FMT == BT_BFP4) wq = lds128(tile + 64 + lane * 16);
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (FMT == BT_BFP8) wv = lds128(tile + 64 + h * 512 + lane * 16);
+    uint2 bx[TG];
+#pragma unroll
+    for (int tg = 0; tg < TG; tg++) bx[tg] = lds64(xs + (TG == 1 ? h * 256 + g * 32 : (tg >> 1) * 1024 + h * 512 + ((tg & 1) * 8 + g) * 32) + t * 8);
+#pragma unroll
+    for (int fs = 0; fs < 2; fs++) {
+      const uint32_t ew = ee[2 * h + fs];
+      const uint32_t s01 = scale_pair<0>(ew), s23 = scale_pair<1>(ew);
+      uint32_t m0, s0, m1, s1;  // magnitude and sign bytes of MMA rows g (channel 2g) and g + 8 (channel 2g + 1)
+      if (FMT == BT_BFP8) {
+        const uint32_t w0 = fs ? wv.z : wv.x, w1 = fs ? wv.w : wv.y;
+        m0 = w0 & 0x7F7F7F7Fu, s0 = w0 & 0x80808080u, m1 = w1 & 0x7F7F7F7Fu, s1 = w1 & 0x80808080u;
+      } else {
+        const uint32_t wb = h ? (fs ? wq.w : wq.z) : (fs ? wq.y : wq.x), wl = wb << 4;
+        m0 = wl & 0x70707070u, s0 = wl & 0x80808080u, m1 = wb & 0x70707070u, s1 = wb & 0x80808080u;
+      }
+      const uint32_t a0 = mul_bf16x2(prmt(m0, s0, 0x5140u), s01), a1 = mul_bf16x2(prmt(m1, s1, 0x5140u), s01);
+      const uint32_t a2 = mul_bf16x2(prmt(m0, s0, 0x7362u), s23), a3 = mul_bf16x2(prmt(m1, s1, 0x7362u), s23);
+#pragma unroll
+      for (int tg = 0; tg < TG; tg++) mma_bf16(acc[fs][tg], a0, a1, a2, a3, bx[tg].x, bx[tg].y);
+    }
+  }
+}
+
+__device__ __forceinline__ float silu(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+__device__ __forceinline__ uint32_t bf16_half_up(float v) { return (__float_as_uint(v) + 0x8000u) >> 16; }
+__device__ __forceinline__ float bf16_value(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+// a beats b: larger value, or the same value at a lower column; -0 equals 0; a NaN never wins
+__device__ __forceinline__ bool beats(float av, int ai, float bv, int bi) { return av > bv || (av == bv && ai < bi); }
+
+
+// The epilogue of one finished tile column. Lane (g, t) holds, for each channel group ng and token group tg,
+// tokens 8 tg + 2t + j (j = 0, 1) and channels 16 ng + 2g + {0, 1}: acc[..][ng][tg][j] and [2 + j].
+template <int NW, int TG>
+__device__ __forceinline__ void finish_column(const GemvParams &p, const float (&acc)[NW][2][TG][4], int col, int cc, int lane,
+                                              float *arg_v, int *arg_i) {
+  const int g = lane >> 2, t = lane & 3;
+  const float unscale = 18446744073709551616.f * p.alpha;  // 2^64: the weights entered the MMA scaled by 2^-64
+  float best_v[TG][2];
+  int best_i[TG][2];
+#pragma unroll
+  for (int tg = 0; tg < TG; tg++) best_v[tg][0] = best_v[tg][1] = -INFINITY, best_i[tg][0] = best_i[tg][1] = 0x7FFFFFFF;
+#pragma unroll
+  for (int ng = 0; ng < 2; ng++) {
+#pragma unroll
+    for (int tg = 0; tg < 4; tg++) {
+      constexpr int kLast = TG - 1;
+      const int tgs = tg < TG ? tg : 0;  // a one-row result repeats across its tile: every row shows token 0
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const int m = 8 * tg + 2 * t + j, at = ((m >> 4) * 2 + ng) * 256 + (m & 15) * 16 + 2 * g;
+        const bool valid = p.M == 1 || (tg <= kLast && m < p.M);
+        float v0 = acc[0][ng][tgs][j] * unscale, v1 = acc[0][ng][tgs][2 + j] * unscale;
+        if (p.add) {
+          const uint32_t a = *reinterpret_cast<const uint32_t *>(p.add + (size_t)col * 1024 + at);
+          v0 += bf16_value((uint16_t)a), v1 += bf16_value((uint16_t)(a >> 16));
+        }
+        if (p.epi == BT_EPI_RELU) v0 = fmaxf(v0, 0.f), v1 = fmaxf(v1, 0.f);
+        else if (p.epi == BT_EPI_SILU) v0 = silu(v0), v1 = silu(v1);
+        else if (NW == 2) v0 = silu(v0) * (acc[NW - 1][ng][tgs][j] * unscale), v1 = silu(v1) * (acc[NW - 1][ng][tgs][2 + j] * unscale);
+        if (p.epi == BT_EPI_ARGMAX) {
+          if (tg <= kLast && m < p.M) {
+            const int n0 = col * 32 + 16 * ng + 2 * g;
+            if (beats(v0, n0, best_v[tgs][j], best_i[tgs][j])) best_v[tgs][j] = v0, best_i[tgs][j] = n0;
+            if (beats(v1, n0 + 1, best_v[tgs][j], best_i[tgs][j])) best_v[tgs][j] = v1, best_i[tgs][j] = n0 + 1;
+          }
+          continue;
+        }
+        if (!valid) v0 = v1 = 0.f;
+        if (p.out_fp32) *reinterpret_cast<float2 *>(static_cast<float *>(p.out) + (size_t)col * 1024 + at) = make_float2(v0, v1);
+        else *reinterpret_cast<uint32_t *>(static_cast<uint16_t *>(p.out) + (size_t)col * 1024 + at) = bf16_half_up(v0) | bf16_half_up(v1) << 16;
+      }
+    }
+  }
+  if (p.epi == BT_EPI_ARGMAX) {
+    // best over this column's 32 channels: combine the lanes that hold the same tokens (same t)
+#pragma unroll
+    for (int tg = 0; tg < 4; tg++) {
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        float v = -INFINITY;
+        int i = 0x7FFFFFFF;
+        if (tg < TG) v = best_v[tg < TG ? tg : 0][j], i = best_i[tg < TG ? tg : 0][j];
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+          const float ov = __shfl_xor_sync(0xFFFFFFFFu, v, d);
+          const int oi = __shfl_xor_sync(0xFFFFFFFFu, i, d);
+          if (beats(ov, oi, v, i)) v = ov, i = oi;
+        }
+        if (g == 0) arg_v[cc * 32 + 8 * tg + 2 * t + j] = v, arg_i[cc * 32 + 8 * tg + 2 * t + j] = i;
+      }
+    }
+  }
+}
+
+template <int FMT, int NW, int TG, int WC>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
+  using C = Config<FMT, NW, TG, WC>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t full0 = sbase, empty0 = sbase + 64;
+  int *flags = reinterpret_cast<int *>(smem + 128);               // [0], [1]: last-arriver verdicts
+  float *arg_v = reinterpret_cast<float *>(smem + 256);           // [16][32] best value per column warp and token
+  int *arg_i = reinterpret_cast<int *>(smem + 256 + 2048);        // [16][32] and its channel
+  float *red = reinterpret_cast<float *>(smem + 4352);
+  const uint32_t stages = sbase + (C::FIXED + 127) / 128 * 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ctas = gridDim.x, cta = blockIdx.x, KT = p.KT;
+  const int subpanels = (p.TC + WC - 1) / WC;
+  const long long units = (long long)subpanels * KT;
+  const long long u0 = range_start(units, cta, ctas), u1 = range_start(units, cta + 1, ctas);
+  int *error = reinterpret_cast<int *>(p.work + kWsError);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.nstages; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kConsumerWarps);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---- producer ----
+    if (lane == 0) {
+      int it = 0;
+      for (long long u = u0; u < u1; it++) {
+        const int sp = (int)(u / KT), kt = (int)(u % KT);
+        const int n = (int)min((long long)C::UPS, min(u1 - u, (long long)(KT - kt)));
+        const int s = it % p.nstages;
+        if (it >= p.nstages && !mbar_wait(empty0 + 8 * s, (it / p.nstages - 1) & 1, kSpinLimit)) atomicExch(error, 1);
+        const int col0 = sp * WC, wcols = min(WC, p.TC - col0);
+        const int run = col0 / kPanel, width = min(kPanel, p.TC - run * kPanel);
+        const uint32_t bar = full0 + 8 * s, stage = stages + s * C::STAGE;
+        mbar_expect_tx(bar, n * (NW * wcols * C::TB + C::XB));
+        for (int i = 0; i < n; i++) {
+          const size_t tile = (size_t)run * kPanel * KT + (size_t)(kt + i) * width + col0 % kPanel;
+#pragma unroll
+          for (int m = 0; m < NW; m++) bulk_g2s(stage + (i * NW + m) * WC * C::TB, p.w[m] + tile * C::TB, wcols * C::TB, bar);
+          const uint8_t *xt = p.x + (size_t)(kt + i) * 2048;
+          const uint32_t xs = stage + C::W_BYTES + i * C::XB;
+          if (TG == 1) bulk_g2s(xs, xt, 256, bar), bulk_g2s(xs + 256, xt + 512, 256, bar);  // rows 0-7 of faces 0 and 1
+          else bulk_g2s(xs, xt, C::XB, bar);
+        }
+        u += n;
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  const int ck = warp / WC, cc = warp % WC, g = lane >> 2, t = lane & 3;
+  float acc[NW][2][TG][4];
+// accumulator i of the lane, with i a compile-time constant after unrolling, so that acc stays in registers
+#define ACC_AT(i) acc[(i) / (8 * TG)][(i) / (4 * TG) % 2][(i) / 4 % TG][(i) % 4]
+#pragma unroll
+  for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
+
+  int it = 0;
+  for (long long u = u0; u < u1; it++) {
+    const int sp = (int)(u / KT), kt = (int)(u % KT);
+    const int n = (int)min((long long)C::UPS, min(u1 - u, (long long)(KT - kt)));
+    const int s = it % p.nstages;
+    if (!mbar_wait(full0 + 8 * s, (it / p.nstages) & 1, kSpinLimit)) atomicExch(error, 2);
+    const uint32_t stage = stages + s * C::STAGE;
+    const int col = sp * WC + cc;
+    if (col < p.TC) {
+      for (int i = ck; i < n; i += C::KS) {
+#pragma unroll
+        for (int m = 0; m < NW; m++) tile_mma<FMT, TG>(stage + ((i * NW + m) * WC + cc) * C::TB, stage + C::W_BYTES + i * C::XB, lane, acc[m]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    u += n;
+    if (u != u1 && u % KT != 0) continue;
+
+    // ---- this CTA is done with sub-panel sp: reduce over k-slices, combine with other CTAs, run the epilogue ----
+    if (C::KS > 1) {
+      for (int r = 1; r < C::KS; r++) {
+        if (ck == r) {
+#pragma unroll
+          for (int i = 0; i < C::ACC; i++) red[(cc * C::ACC + i) * 32 + lane] = ACC_AT(i);
+        }
+        named_barrier(1, kConsumerWarps * 32);
+        if (ck == 0) {
+#pragma unroll
+          for (int i = 0; i < C::ACC; i++) ACC_AT(i) += red[(cc * C::ACC + i) * 32 + lane];
+        }
+        named_barrier(1, kConsumerWarps * 32);
+      }
+    }
+    const int first = cta_of((long long)sp * KT, units, ctas), last = cta_of((long long)(sp + 1) * KT - 1, units, ctas);
+    bool finish = true;
+    if (first != last) {
+      float *partials = reinterpret_cast<float *>(p.work + kWsPartials);
+      int *counter = reinterpret_cast<int *>(p.work + kWsCounters) + sp;
+      const int mine = cta * 2 + (sp == (int)(u0 / KT) ? 0 : 1);
+      if (ck == 0) {
+        float4 *slot = reinterpret_cast<float4 *>(partials + (size_t)mine * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
+#pragma unroll
+        for (int i = 0; i < C::ACC / 4; i++)
+          slot[i * 32 + lane] = make_float4(ACC_AT(4 * i), ACC_AT(4 * i + 1), ACC_AT(4 * i + 2), ACC_AT(4 * i + 3));
+        __threadfence();
+      }
+      named_barrier(1, kConsumerWarps * 32);
+      if (threadIdx.x == 0) flags[0] = atomicAdd(counter, 1) == last - first;
+      named_barrier(1, kConsumerWarps * 32);
+      finish = flags[0] != 0;
+      if (finish) {
+        __threadfence();
+        if (ck == 0) {
+#pragma unroll
+          for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
+          for (int c = first; c <= last; c++) {  // always in CTA order: the sum does not depend on who arrived last
+            const int theirs = c * 2 + (sp == (int)(range_start(units, c, ctas) / KT) ? 0 : 1);
+            const float4 *slot = reinterpret_cast<const float4 *>(partials + (size_t)theirs * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
+#pragma unroll
+            for (int i = 0; i < C::ACC / 4; i++) {
+              const float4 v = __ldcg(slot + i * 32 + lane);
+              ACC_AT(4 * i) += v.x, ACC_AT(4 * i + 1) += v.y, ACC_AT(4 * i + 2) += v.z, ACC_AT(4 * i + 3) += v.w;
+            }
+          }
+        }
+        if (threadIdx.x == 0) *counter = 0;  // ready for the next launch
+      }
+    }
+
+    if (finish && ck == 0 && col < p.TC) finish_column<NW, TG>(p, acc, col, cc, lane, arg_v, arg_i);
+    if (p.epi == BT_EPI_ARGMAX && finish) {
+      // the sub-panel's best per token, then, in the last sub-panel to finish, the best over all sub-panels in order
+      named_barrier(1, kConsumerWarps * 32);
+      float *part_v = reinterpret_cast<float *>(p.work + kWsArgVal);
+      int *part_i = reinterpret_cast<int *>(p.work + kWsArgIdx);
+      const int wcols = min(WC, p.TC - sp * WC);
+      if (warp == 0) {
+        float v = arg_v[lane];
+        int i = arg_i[lane];
+        for (int c = 1; c < wcols; c++)
+          if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
+        part_v[sp * 32 + lane] = v, part_i[sp * 32 + lane] = i;
+        __threadfence();
+      }
+      named_barrier(1, kConsumerWarps * 32);
+      int *done = reinterpret_cast<int *>(p.work + kWsPanelsDone);
+      if (threadIdx.x == 0) flags[1] = atomicAdd(done, 1) == subpanels - 1;
+      named_barrier(1, kConsumerWarps * 32);
+      if (flags[1]) {
+        __threadfence();
+        if (warp == 0 && lane < p.M) {
+          float v = -INFINITY;
+          int i = 0x7FFFFFFF;
+          for (int q = 0; q < subpanels; q++) {
+            const float ov = __ldcg(part_v + q * 32 + lane);
+            const int oi = __ldcg(part_i + q * 32 + lane);
+            if (beats(ov, oi, v, i)) v = ov, i = oi;
+          }
+          p.arg_val[lane] = v, p.arg_idx[lane] = i + p.arg_base;
+        }
+        if (threadIdx.x == 0) *done = 0;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
+  }
+#undef ACC_AT
+}
+
+// ---- host side: pick a configuration, size shared memory, launch ----
+
+int g_wc[3] = {4, 8, 16};  // tile columns per sub-panel for 1, 2 and 4 token groups
+int g_stages = 0;          // 0: as many as fit
+
+template <int FMT, int NW, int TG, int WC>
+int launch(const GemvParams &base, int sms, cudaStream_t stream) {
+  using C = Config<FMT, NW, TG, WC>;
+  GemvParams p = base;
+  int fit = (kSmemBudget - (C::FIXED + 127) / 128 * 128) / C::STAGE;
+  p.nstages = min(kMaxStages, g_stages > 0 ? min(g_stages, fit) : fit);
+  if (p.nstages < 2) return fail(BT_DEVICE, "bt_gemv_bfp: a stage of %d bytes leaves room for %d stages", C::STAGE, p.nstages);
+  const int smem = (C::FIXED + 127) / 128 * 128 + p.nstages * C::STAGE;
+  static bool configured[64] = {};
+  int device = 0;
+  BT_CUDA(cudaGetDevice(&device));
+  if (!configured[device & 63]) {
+    BT_CUDA(cudaFuncSetAttribute(gemv_kernel<FMT, NW, TG, WC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    configured[device & 63] = true;
+  }
+  const long long units = (long long)((p.TC + WC - 1) / WC) * p.KT;
+  const int ctas = (int)min((long long)min(sms, kMaxCtas), units);
+  gemv_kernel<FMT, NW, TG, WC><<<ctas, kThreads, smem, stream>>>(p);
+  return launched("gemv_kernel");
+}
+
+template <int FMT, int NW, int TG>
+int launch_wc(const GemvParams &p, int wc, int sms, cudaStream_t stream) {
+  if (wc == 4) return launch<FMT, NW, TG, 4>(p, sms, stream);
+  if (wc == 8) return launch<FMT, NW, TG, 8>(p, sms, stream);
+  return launch<FMT, NW, TG, 16>(p, sms, stream);
+}
+
+template <int FMT, int NW>
+int launch_tg(const GemvParams &p, int sms, cudaStream_t stream) {
+  if (p.M <= 8) return launch_wc<FMT, NW, 1>(p, g_wc[0], sms, stream);
+  if (p.M <= 16) return launch_wc<FMT, NW, 2>(p, g_wc[1], sms, stream);
+  return launch_wc<FMT, NW, 4>(p, g_wc[2], sms, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int bt_gemv_workspace_bytes(int device, size_t *bytes) {
+  BT_REQUIRE(bytes, "bt_gemv_workspace_bytes: null result");
+  (void)device;
+  *bytes = kWsBytes;
+  return BT_OK;
+}
+
+// Tuning knobs for experiments: tile columns per sub-panel (4, 8 or 16) for up to 8, 16 and 32 token rows, and the
+// number of pipeline stages (0 = as many as fit). Values of 0 keep the current setting.
+int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages) {
+  const int wc[3] = {wc_m8, wc_m16, wc_m32};
+  for (int i = 0; i < 3; i++) {
+    BT_REQUIRE(wc[i] == 0 || wc[i] == 4 || wc[i] == 8 || wc[i] == 16, "bt_gemv_tune: sub-panel width must be 4, 8 or 16, not %d", wc[i]);
+    if (wc[i]) g_wc[i] = wc[i];
+  }
+  BT_REQUIRE(stages >= 0 && stages <= kMaxStages, "bt_gemv_tune: stages must be 0..%d", kMaxStages);
+  g_stages = stages;
+  return BT_OK;
+}
+
+int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2, uint64_t add,
+                float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base, uint64_t work,
+                size_t work_bytes, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_gemv_bfp: weights must be bfp8 (8) or bfp4 (4), not %d", fmt);
+  BT_REQUIRE(epilogue >= BT_EPI_NONE && epilogue <= BT_EPI_ARGMAX, "bt_gemv_bfp: unknown epilogue %d", epilogue);
+  BT_REQUIRE(M >= 1 && M <= 32, "bt_gemv_bfp: takes 1 to 32 rows of x, not %d", M);
+  BT_REQUIRE(K > 0 && N > 0 && K % 32 == 0 && N % 32 == 0, "bt_gemv_bfp: K and N must be positive multiples of 32: %d x %d", K, N);
+  BT_REQUIRE(x && w && x % 16 == 0 && w % 16 == 0, "bt_gemv_bfp: x and w must be 16-byte aligned device addresses");
+  BT_REQUIRE((epilogue == BT_EPI_GLU) == (w2 != 0) && w2 % 16 == 0, "bt_gemv_bfp: w2 goes with the GLU epilogue, and only with it");
+  BT_REQUIRE(add % 4 == 0, "bt_gemv_bfp: the addend must be 4-byte aligned");
+  if (epilogue == BT_EPI_ARGMAX) BT_REQUIRE(arg_val && arg_idx, "bt_gemv_bfp: the argmax epilogue needs arg_val and arg_idx");
+  else BT_REQUIRE(out && out % 8 == 0 && (out_dtype == BT_BF16 || out_dtype == BT_FP32), "bt_gemv_bfp: needs an 8-byte aligned bf16 or fp32 result");
+  BT_REQUIRE(work && work % 16 == 0 && work_bytes >= kWsBytes, "bt_gemv_bfp: needs %zu bytes of 16-byte aligned scratch, got %zu", kWsBytes, work_bytes);
+  BT_REQUIRE((N / 32 + 3) / 4 <= kMaxSubPanels, "bt_gemv_bfp: N = %d is past the %d columns one launch handles", N, kMaxSubPanels * 128);
+  if (int s = use_device(device)) return s;
+  int sms = 0;
+  BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  GemvParams p{};
+  p.x = as_ptr<uint8_t>(x), p.w[0] = as_ptr<uint8_t>(w), p.w[1] = as_ptr<uint8_t>(w2), p.add = as_ptr<uint16_t>(add);
+  p.out = as_ptr<void>(out), p.arg_val = as_ptr<float>(arg_val), p.arg_idx = as_ptr<int>(arg_idx), p.work = as_ptr<uint8_t>(work);
+  p.alpha = alpha, p.arg_base = arg_base, p.M = M, p.KT = K / 32, p.TC = N / 32, p.epi = epilogue, p.out_fp32 = out_dtype == BT_FP32;
+  cudaStream_t st = as_stream(stream);
+  if (fmt == BT_BFP8) return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP8, 2>(p, sms, st) : launch_tg<BT_BFP8, 1>(p, sms, st);
+  return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP4, 2>(p, sms, st) : launch_tg<BT_BFP4, 1>(p, sms, st);
+}
+
+// Nonzero once a bounded wait inside a launch that used this scratch gave up; the results of that launch are
+// then unreliable. Reads the flag back (synchronising the stream) and clears it.
+int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error) {
+  BT_REQUIRE(work && error, "bt_gemv_check: null argument");
+  if (int s = use_device(device)) return s;
+  BT_CUDA(cudaMemcpyAsync(error, as_ptr<void>(work + kWsError), 4, cudaMemcpyDeviceToHost, as_stream(stream)));
+  BT_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  if (*error) BT_CUDA(cudaMemsetAsync(as_ptr<void>(work + kWsError), 0, 4, as_stream(stream)));
+  return BT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,255 @@
+// Tile layout and block-float conversion kernels: the byte and integer work either side of the matmul.
+// All of it is HBM-bound; every kernel moves 16 bytes per thread per access and touches each byte once.
+#include "common.cuh"
+#include "stream_layout.cuh"
+
+using namespace bt;
+
+namespace {
+
+constexpr int kThreads = 256;
+inline unsigned blocks_for(size_t items) { return (unsigned)((items + kThreads - 1) / kThreads); }
+
+// ---- tilize / untilize ------------------------------------------------------------------------------------
+// One thread moves half a run: 8 consecutive datums of a face row (16 bytes of bf16, 32 of fp32).
+// Datum (r, c) of a tile is at (r / 16 * 2 + c / 16) * 256 + r % 16 * 16 + c % 16.
+template <typename T>
+__global__ void tilize_kernel(const T *__restrict__ src, T *__restrict__ dst, int batch, int rows, int cols, int tr, int tc) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;          // half-run index in the tiled image
+  size_t total = (size_t)batch * tr * tc * 128;
+  if (i >= total) return;
+  size_t tile = i / 128;
+  int h = (int)(i % 128), face = h / 32, r16 = h % 32 / 2, c8 = h % 2 * 8;
+  int b = (int)(tile / ((size_t)tr * tc)), ti = (int)(tile / tc % tr), tj = (int)(tile % tc);
+  int r = ti * 32 + face / 2 * 16 + r16, c0 = tj * 32 + face % 2 * 16 + c8;
+  if (rows == 1) r = 0;                                              // a single row fills its tile
+  __align__(16) T out[8];
+  const T *row = src + ((size_t)b * rows + r) * cols;
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    int c = cols == 1 ? 0 : c0 + k;                                  // a single column repeats
+    out[k] = (r < rows && c < cols) ? row[c] : T(0);
+  }
+  uint4 *o = reinterpret_cast<uint4 *>(dst + i * 8);
+#pragma unroll
+  for (int k = 0; k < (int)(sizeof(out) / 16); k++) o[k] = reinterpret_cast<const uint4 *>(out)[k];
+}
+
+template <typename T>
+__global__ void untilize_kernel(const T *__restrict__ src, T *__restrict__ dst, int batch, int rows, int cols, int tr, int tc) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t total = (size_t)batch * tr * tc * 128;
+  if (i >= total) return;
+  size_t tile = i / 128;
+  int h = (int)(i % 128), face = h / 32, r16 = h % 32 / 2, c8 = h % 2 * 8;
+  int b = (int)(tile / ((size_t)tr * tc)), ti = (int)(tile / tc % tr), tj = (int)(tile % tc);
+  int r = ti * 32 + face / 2 * 16 + r16, c0 = tj * 32 + face % 2 * 16 + c8;
+  if (r >= rows) return;
+  __align__(16) T in[8];
+#pragma unroll
+  for (int k = 0; k < (int)(sizeof(in) / 16); k++) reinterpret_cast<uint4 *>(in)[k] = reinterpret_cast<const uint4 *>(src + i * 8)[k];
+  T *row = dst + ((size_t)b * rows + r) * cols;
+#pragma unroll
+  for (int k = 0; k < 8; k++)
+    if (c0 + k < cols) row[c0 + k] = in[k];
+}
+
+// fp32 bits -> bf16 bits, round to nearest even; a NaN keeps a quiet payload.
+__global__ void round_bf16_kernel(const uint32_t *__restrict__ src, uint16_t *__restrict__ dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t b = src[i];
+  dst[i] = (b & 0x7FFFFFFFu) > 0x7F800000u ? (uint16_t)(b >> 16 | 0x40) : (uint16_t)((b + 0x7FFFu + (b >> 16 & 1)) >> 16);
+}
+
+// ---- pack ---------------------------------------------------------------------------------------------------
+// One thread packs one run: the 16 datums of a face row share their largest exponent field.
+// bfp8: q = min((m + (1 << s)) >> (s + 1), 127) with s = min(top - e, 8); byte = q ? sign << 7 | q : 0.
+// bfp4: q = s < 4 ? min((m + (16 << s)) >> (s + 5), 7) : 0; nibble = q ? sign << 3 | q : 0, even datum low.
+template <int FMT>
+__global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__ dst, size_t runs) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= runs) return;
+  uint4 lo = src[2 * i], hi = src[2 * i + 1];
+  uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  uint32_t top = 0;
+#pragma unroll
+  for (int k = 0; k < 8; k++) top = max(top, max(w[k] >> 7 & 255u, w[k] >> 23 & 255u));
+  uint32_t q[16];
+#pragma unroll
+  for (int k = 0; k < 16; k++) {
+    uint32_t b = (w[k / 2] >> (16 * (k % 2))) & 0xFFFFu, e = b >> 7 & 255u, m = (b & 127u) | (e ? 128u : 0u), d = top - e;
+    if (FMT == BT_BFP8) {
+      uint32_t s = min(d, 8u), v = min((m + (1u << s)) >> (s + 1), 127u);
+      q[k] = v ? (b >> 15) << 7 | v : 0u;
+    } else {
+      uint32_t s = min(d, 4u), v = d < 4 ? min((m + (16u << s)) >> (s + 5), 7u) : 0u;
+      q[k] = v ? (b >> 15) << 3 | v : 0u;
+    }
+  }
+  constexpr size_t TB = tile_bytes(FMT);
+  uint8_t *tile = dst + i / 64 * TB;
+  int r = (int)(i % 64);
+  tile[r] = (uint8_t)top;
+  if (FMT == BT_BFP8) {
+    uint4 o;
+    o.x = q[0] | q[1] << 8 | q[2] << 16 | q[3] << 24;
+    o.y = q[4] | q[5] << 8 | q[6] << 16 | q[7] << 24;
+    o.z = q[8] | q[9] << 8 | q[10] << 16 | q[11] << 24;
+    o.w = q[12] | q[13] << 8 | q[14] << 16 | q[15] << 24;
+    *reinterpret_cast<uint4 *>(tile + 64 + r * 16) = o;
+  } else {
+    uint2 o;
+    o.x = q[0] | q[1] << 4 | q[2] << 8 | q[3] << 12 | q[4] << 16 | q[5] << 20 | q[6] << 24 | q[7] << 28;
+    o.y = q[8] | q[9] << 4 | q[10] << 8 | q[11] << 12 | q[12] << 16 | q[13] << 20 | q[14] << 24 | q[15] << 28;
+    *reinterpret_cast<uint2 *>(tile + 64 + r * 8) = o;
+  }
+}
+
+// ---- unpack --------------------------------------------------------------------------------------------------
+// x = value byte (bfp4: nibble << 4). A zero magnitude is 0, or -inf (0xFF80) with the sign set. Otherwise the
+// magnitude is normalised: m = (x & 127) << 1, s = 8 - bit_length(m), bf16 = sign | ((e - s) mod 256) << 7 | (m << s) & 0x7E.
+__device__ __forceinline__ uint32_t decode_bfp(uint32_t x, uint32_t e) {
+  uint32_t mag = x & 127u;
+  if (!mag) return x >> 7 ? 0xFF80u : 0u;
+  uint32_t m = mag << 1, s = __clz(m) - 24;     // 8 - bit_length(m)
+  return (x >> 7) << 15 | ((e - s) & 255u) << 7 | ((m << s) & 0x7Eu);
+}
+
+template <int FMT>
+__global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict__ dst, size_t runs) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= runs) return;
+  constexpr size_t TB = tile_bytes(FMT);
+  const uint8_t *tile = src + i / 64 * TB;
+  int r = (int)(i % 64);
+  uint32_t e = tile[r], x[16];
+  if (FMT == BT_BFP8) {
+    uint4 v = *reinterpret_cast<const uint4 *>(tile + 64 + r * 16);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 16; k++) x[k] = w[k / 4] >> (8 * (k % 4)) & 255u;
+  } else {
+    uint2 v = *reinterpret_cast<const uint2 *>(tile + 64 + r * 8);
+    uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+    for (int k = 0; k < 16; k++) x[k] = (w[k / 8] >> (4 * (k % 8)) & 15u) << 4;
+  }
+  uint32_t o[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) o[k] = decode_bfp(x[2 * k], e) | decode_bfp(x[2 * k + 1], e) << 16;
+  dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// ---- canonical <-> streaming layout ---------------------------------------------------------------------------
+// One block moves one tile through shared memory. To the stream: read the canonical tile in 16-byte pieces,
+// scatter its bytes to their streamed positions, write the streamed tile in 16-byte pieces. Back: the reverse.
+template <int FMT, bool TO_STREAM>
+__global__ void relayout_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
+  constexpr int TB = tile_bytes(FMT), PIECES = TB / 16;
+  __shared__ __align__(16) uint8_t tile[TB];
+  int ti = blockIdx.x / tc, tj = blockIdx.x % tc;
+  size_t canonical = ((size_t)ti * tc + tj) * TB, streamed = stream_tile_index(ti, tj, tr, tc) * (size_t)TB;
+  int p = threadIdx.x;
+  if (TO_STREAM) {
+    if (p < PIECES) {
+      uint4 v = *reinterpret_cast<const uint4 *>(src + canonical + p * 16);
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 16; k++) tile[stream_pos<FMT>(p * 16 + k)] = (uint8_t)(w[k / 4] >> (8 * (k % 4)));
+    }
+    __syncthreads();
+    if (p < PIECES) *reinterpret_cast<uint4 *>(dst + streamed + p * 16) = *reinterpret_cast<const uint4 *>(tile + p * 16);
+  } else {
+    if (p < PIECES) *reinterpret_cast<uint4 *>(tile + p * 16) = *reinterpret_cast<const uint4 *>(src + streamed + p * 16);
+    __syncthreads();
+    if (p < PIECES) {
+      uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int k = 0; k < 16; k++) w[k / 4] |= (uint32_t)tile[stream_pos<FMT>(p * 16 + k)] << (8 * (k % 4));
+      *reinterpret_cast<uint4 *>(dst + canonical + p * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+int check_shape(const char *what, int batch, int rows, int cols) {
+  BT_REQUIRE(batch > 0 && rows > 0 && cols > 0, "%s: tensor dimensions must be positive: %d x %d x %d", what, batch, rows, cols);
+  return BT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int bt_tilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, int rows, int cols, uint64_t stream) {
+  if (int s = check_shape("bt_tilize", batch, rows, cols)) return s;
+  BT_REQUIRE(itemsize == 2 || itemsize == 4, "bt_tilize: itemsize must be 2 or 4, not %d", itemsize);
+  BT_REQUIRE(src && dst, "bt_tilize: null device address");
+  if (int s = use_device(device)) return s;
+  int tr = (rows + 31) / 32, tc = (cols + 31) / 32;
+  size_t items = (size_t)batch * tr * tc * 128;
+  if (itemsize == 2) tilize_kernel<uint16_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
+  else tilize_kernel<uint32_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+  return launched("tilize_kernel");
+}
+
+int bt_untilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, int rows, int cols, uint64_t stream) {
+  if (int s = check_shape("bt_untilize", batch, rows, cols)) return s;
+  BT_REQUIRE(itemsize == 2 || itemsize == 4, "bt_untilize: itemsize must be 2 or 4, not %d", itemsize);
+  BT_REQUIRE(src && dst, "bt_untilize: null device address");
+  if (int s = use_device(device)) return s;
+  int tr = (rows + 31) / 32, tc = (cols + 31) / 32;
+  size_t items = (size_t)batch * tr * tc * 128;
+  if (itemsize == 2) untilize_kernel<uint16_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
+  else untilize_kernel<uint32_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+  return launched("untilize_kernel");
+}
+
+int bt_round_bf16(int device, uint64_t src_f32, uint64_t dst_bf16, size_t count, uint64_t stream) {
+  BT_REQUIRE(src_f32 && dst_bf16 && count, "bt_round_bf16: null device address or zero count");
+  if (int s = use_device(device)) return s;
+  round_bf16_kernel<<<blocks_for(count), kThreads, 0, as_stream(stream)>>>(as_ptr<uint32_t>(src_f32), as_ptr<uint16_t>(dst_bf16), count);
+  return launched("round_bf16_kernel");
+}
+
+int bt_pack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_pack_bfp: format must be bfp8 (8) or bfp4 (4), not %d", fmt);
+  BT_REQUIRE(src && dst && ntiles, "bt_pack_bfp: null device address or zero tiles");
+  BT_REQUIRE(src % 16 == 0 && dst % 16 == 0, "bt_pack_bfp: tiles must be 16-byte aligned");
+  if (int s = use_device(device)) return s;
+  size_t runs = ntiles * 64;
+  if (fmt == BT_BFP8) pack_kernel<BT_BFP8><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint4>(src), as_ptr<uint8_t>(dst), runs);
+  else pack_kernel<BT_BFP4><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint4>(src), as_ptr<uint8_t>(dst), runs);
+  return launched("pack_kernel");
+}
+
+int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_unpack_bfp: format must be bfp8 (8) or bfp4 (4), not %d", fmt);
+  BT_REQUIRE(src && dst && ntiles, "bt_unpack_bfp: null device address or zero tiles");
+  BT_REQUIRE(src % 16 == 0 && dst % 16 == 0, "bt_unpack_bfp: tiles must be 16-byte aligned");
+  if (int s = use_device(device)) return s;
+  size_t runs = ntiles * 64;
+  if (fmt == BT_BFP8) unpack_kernel<BT_BFP8><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint8_t>(src), as_ptr<uint4>(dst), runs);
+  else unpack_kernel<BT_BFP4><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint8_t>(src), as_ptr<uint4>(dst), runs);
+  return launched("unpack_kernel");
+}
+
+int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols, uint64_t src, uint64_t dst, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_relayout: format must be bfp8 (8) or bfp4 (4), not %d", fmt);
+  BT_REQUIRE(tile_rows > 0 && tile_cols > 0, "bt_relayout: tile counts must be positive: %d x %d", tile_rows, tile_cols);
+  BT_REQUIRE((long long)tile_rows * tile_cols < (1ll << 31), "bt_relayout: too many tiles for one launch");
+  BT_REQUIRE(src && dst && src != dst && src % 16 == 0 && dst % 16 == 0, "bt_relayout: needs distinct 16-byte aligned buffers");
+  if (int s = use_device(device)) return s;
+  unsigned blocks = (unsigned)(tile_rows * tile_cols);
+  cudaStream_t st = as_stream(stream);
+  const uint8_t *s8 = as_ptr<uint8_t>(src);
+  uint8_t *d8 = as_ptr<uint8_t>(dst);
+  if (fmt == BT_BFP8 && to_stream) relayout_kernel<BT_BFP8, true><<<blocks, 96, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else if (fmt == BT_BFP8) relayout_kernel<BT_BFP8, false><<<blocks, 96, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else if (to_stream) relayout_kernel<BT_BFP4, true><<<blocks, 64, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else relayout_kernel<BT_BFP4, false><<<blocks, 64, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  return launched("relayout_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,45 @@
+// The streaming layout of block-float weights (what Tensor.columns() produces on this backend).
+//
+// A matrix of tr x tc tiles is stored as runs of kPanel tile columns. Inside a run the tiles go tile row by
+// tile row, the run's tiles of one tile row side by side, so the tiles a CTA needs for consecutive K are one
+// contiguous range. Inside a tile the 64 exponent bytes still come first, then the values, but both are
+// permuted so that each lane of a warp fetches exactly the bytes of its MMA fragment with 128-bit loads:
+//
+//   exponents  position t*16 + face*4 + kk            holds the exponent of datum row k = 4t + kk of face `face`
+//   bfp8       position 64 + h*512 + lane*16 + fs*8 + ns*4 + kk
+//              holds datum (k = 16h + 4t + kk, n = 16fs + 2g + ns), lane = 4g + t
+//   bfp4       position 64 + lane*16 + h*8 + fs*4 + kk
+//              holds the byte with datums (k = 16h + 4t + kk, n = 16fs + 2g) low nibble, (.., n + 1) high
+//
+// with face = 2h + fs, k the row (input channel) and n the column (output channel) inside the tile. It is a
+// pure permutation of bytes: no byte is changed, duplicated or padded.
+#pragma once
+#include <cstddef>
+#include "../../include/baretile_b200.h"
+
+namespace bt {
+
+constexpr int kPanel = 16;  // tile columns in a run
+
+// Position in the streamed tile of canonical byte c.
+template <int FMT>
+__host__ __device__ inline int stream_pos(int c) {
+  if (c < 64) return (c % 16 / 4) * 16 + (c / 16) * 4 + c % 4;
+  int i = c - 64;
+  if (FMT == BT_BFP8) {
+    int face = i / 256, k = i / 16 % 16, n = i % 16;
+    int lane = (n / 2) * 4 + k / 4;
+    return 64 + (face / 2) * 512 + lane * 16 + (face % 2) * 8 + (n % 2) * 4 + k % 4;
+  }
+  int face = i / 128, k = i / 8 % 16, g = i % 8;
+  int lane = g * 4 + k / 4;
+  return 64 + lane * 16 + (face / 2) * 8 + (face % 2) * 4 + k % 4;
+}
+
+// Index, in tiles, of tile (ti, tj) of a tr x tc matrix in the streamed order.
+__host__ __device__ inline size_t stream_tile_index(int ti, int tj, int tr, int tc) {
+  int run = tj / kPanel, width = tc - run * kPanel < kPanel ? tc - run * kPanel : kPanel;
+  return (size_t)run * kPanel * tr + (size_t)ti * width + tj % kPanel;
+}
+
+}  // namespace bt

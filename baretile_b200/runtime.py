@@ -1,0 +1,247 @@
+"""Queue work on a device: the CUDA stand-in for the reference's Runtime (baretile/runtime.py:543-923).
+
+The reference's Runtime owns a rectangle of workers, a command ring in host memory, a DRAM hole allocator with
+deferred frees, and per-launch timing records. Here one CUDA stream plays the ring (launches run in order,
+asynchronously; `wait` blocks), device memory comes from arenas carved by the same first-fit hole allocator
+(64-byte granularity there, 256 here), and timing records are CUDA events. Frees need no deferral: every access
+to device memory is queued on the runtime's stream, so memory released now is reused only by work queued later.
+"""
+import collections, ctypes, time
+from baretile_b200 import _lib
+
+ALIGN = 256            # allocation granularity in bytes
+ARENA = 1 << 30        # device memory is taken from the driver in pieces of at least this size
+TIMES = 1024           # launches whose timing records are kept (baretile/runtime.py: TIMES)
+
+
+class Bound(int):
+  """A launch argument a replay can replace (baretile/runtime.py:476-482). Kept for interface parity."""
+  def __new__(cls, value, key):
+    self = super().__new__(cls, value)
+    self.key = key
+    return self
+
+
+def _merge_holes(holes):
+  holes.sort()
+  merged = []
+  for addr, room in holes:
+    if merged and merged[-1][0] + merged[-1][1] == addr: merged[-1] = (merged[-1][0], merged[-1][1] + room)
+    else: merged.append((addr, room))
+  holes[:] = merged
+
+
+class Recording:
+  """Launches recorded once and replayed with one call: the reference's Recording / tensor.jit
+  (baretile/tensor.py:1171-1293), which replays a block of commands with one doorbell write. Here the block is a
+  CUDA graph. Recorded launches keep their addresses, so the tensors they use must stay alive.
+
+      with rt.record() as step: y = (x @ w).relu().realize()
+      step.replay()
+  """
+  def __init__(self, rt): self.rt, self.graph, self.count = rt, None, 0
+  def __enter__(self):
+    self.rt.check()
+    self.first = self.rt.launches
+    _lib.call("bt_graph_begin", self.rt.device, self.rt.stream)
+    return self
+  def __exit__(self, kind, *_):
+    graph = ctypes.c_uint64()
+    try: _lib.call("bt_graph_end", self.rt.device, self.rt.stream, ctypes.byref(graph))
+    except Exception:
+      if kind is None: raise
+      return
+    self.graph, self.count = graph.value, self.rt.launches - self.first
+  def replay(self):
+    self.rt.check()
+    if self.graph is None: raise RuntimeError("nothing was recorded")
+    _lib.call("bt_graph_launch", self.rt.device, self.graph, self.rt.stream)
+    self.rt.launches += self.count
+  def close(self):
+    if self.graph is not None and self.rt.active: _lib.lib().bt_graph_destroy(self.rt.device, self.graph)
+    self.graph = None
+
+
+class Runtime:
+  """Run kernels on one CUDA device, in order. A new Runtime on a chip closes the chip's older runtime, as an
+  overlapping rectangle does in the reference (baretile/runtime.py:593-598). Close a runtime to release its
+  memory; a closed runtime cannot be reused."""
+  def __init__(self, chip, start=None, end=None, ring=1 << 20, timing=False):
+    if ring < 64 or ring & (ring - 1): raise ValueError("ring size must be a power of two, at least 64 bytes")
+    self.chip, self.device, self.launches = chip, chip.device, 0
+    self.cores = list(chip.tensix)
+    self.grid = (list(range(len(self.cores))), [0])
+    self.start, self.end = start or self.cores[0], end or self.cores[-1]
+    self.active, self.timing = False, timing
+    self.holes, self.used, self.arenas = [], {}, []
+    self.sent = {}                                   # launch number % TIMES -> (name, start event, end event)
+    self.numbers = {}                                # 1 x 1 tensors of Python numbers, made once
+    self.log = None
+    self.stream = ctypes.c_uint64()
+    for other in list(chip.taken.values()): other.close()
+    _lib.call("bt_stream_create", self.device, ctypes.byref(self.stream))
+    self.stream = self.stream.value
+    self.active = True
+    chip.taken[id(self)] = self
+    try:
+      size = ctypes.c_size_t()
+      _lib.call("bt_gemv_workspace_bytes", self.device, ctypes.byref(size))
+      self.work_bytes = size.value
+      self.work = self.dram_alloc(self.work_bytes)
+      _lib.call("bt_memset", self.device, self.work, 0, self.work_bytes, self.stream)
+    except BaseException:
+      self.close()
+      raise
+
+  # ---- lifetime ----
+  def check(self):
+    """Reject work after explicit shutdown or takeover by another runtime (baretile/runtime.py:645-647)."""
+    if not self.active: raise RuntimeError("runtime is closed or was replaced by an overlapping runtime")
+
+  def close(self):
+    """Finish queued work and release the device memory. Closing twice is harmless (baretile/runtime.py:649-653)."""
+    if not self.active: return
+    self.active = False
+    try: _lib.call("bt_stream_sync", self.device, self.stream, 2000)
+    except (TimeoutError, RuntimeError): pass
+    for _, start, end in self.sent.values():
+      for e in (start, end):
+        if e: _lib.lib().bt_event_destroy(self.device, e)
+    self.sent.clear()
+    for ptr in getattr(self, "pinned", []): _lib.lib().bt_host_free(ptr)
+    self.pinned = []
+    for addr, _ in self.arenas: _lib.lib().bt_free(self.device, addr)
+    self.arenas, self.holes = [], []
+    self.used.clear()
+    _lib.lib().bt_stream_destroy(self.device, self.stream)
+    self.chip.taken.pop(id(self), None)
+
+  @property
+  def closed(self): return not self.active
+  def __enter__(self): self.check(); return self
+  def __exit__(self, *_): self.close()
+  def __del__(self):
+    try: self.close()
+    except Exception: pass
+
+  # ---- launches ----
+  def launch(self, kernel, args=(), units=None, name=""):
+    """Queue a kernel: here `kernel` is the name of a C-ABI entry point and `args` its arguments after the device
+    and before the stream (reference: a compiled kernel image and its words, baretile/runtime.py:680-697). `units`
+    is accepted for parity; the entry point sizes its own grid."""
+    self.check()
+    if units is not None and not 1 <= int(units) < 2**32: raise ValueError("launch units must be in [1, 2**32 - 1]")
+    if self.log is not None: self.log.append((kernel, args, units, name))
+    start = end = 0
+    if self.timing:
+      start, end = ctypes.c_uint64(), ctypes.c_uint64()
+      _lib.call("bt_event_create", self.device, ctypes.byref(start))
+      _lib.call("bt_event_create", self.device, ctypes.byref(end))
+      start, end = start.value, end.value
+      _lib.call("bt_event_record", self.device, start, self.stream)
+    _lib.call(kernel, self.device, *args, self.stream)
+    if self.timing: _lib.call("bt_event_record", self.device, end, self.stream)
+    self.launches += 1
+    old = self.sent.pop(self.launches % TIMES, None)
+    if old:
+      for e in old[1:]:
+        if e: _lib.lib().bt_event_destroy(self.device, e)
+    self.sent[self.launches % TIMES] = (name or kernel, start, end)
+
+  def wait(self, timeout=60, launch=None):
+    """Block until the queued launches are done (baretile/runtime.py:858-880). On timeout raise TimeoutError; the
+    runtime stays usable. Also raises RuntimeError if a kernel reported that one of its bounded waits gave up."""
+    self.check()
+    if launch is not None and launch > self.launches:
+      raise ValueError(f"launch {launch} was never queued; the last one queued is {self.launches}")
+    _lib.call("bt_stream_sync", self.device, self.stream, int(timeout * 1000))
+    error = ctypes.c_int()
+    _lib.call("bt_gemv_check", self.device, self.work, self.stream, ctypes.byref(error))
+    if error.value: raise RuntimeError(f"a matmul launch gave up on a bounded wait (code {error.value}); its results are unreliable")
+
+  def finished(self):
+    done = ctypes.c_int()
+    _lib.call("bt_stream_query", self.device, self.stream, ctypes.byref(done))
+    return self.launches if done.value else max(self.launches - 1, 0)
+
+  def profile(self, since):
+    """Wait, then [(name, launches, microseconds, None)] for the launches after `since`, grouped by name, longest
+    first (baretile/runtime.py:773-786 returns cycles and NoC bytes). Times need Runtime(timing=True)."""
+    self.wait()
+    if self.launches - since > TIMES: raise ValueError(f"{self.launches - since} launches to profile, but only the last {TIMES} are kept")
+    totals = collections.defaultdict(lambda: [0, 0.0])
+    for n in range(since + 1, self.launches + 1):
+      if n % TIMES not in self.sent: continue   # a replayed launch has no record of its own
+      name, start, end = self.sent[n % TIMES]
+      ms = ctypes.c_float()
+      if start: _lib.call("bt_event_elapsed_ms", self.device, start, end, ctypes.byref(ms))
+      totals[name][0] += 1
+      totals[name][1] += ms.value * 1e3
+    return sorted(((name, n, us if self.timing else None, None) for name, (n, us) in totals.items()), key=lambda r: -(r[2] or 0))
+
+  # ---- device memory ----
+  def dram_alloc(self, size):
+    """First free hole that is big enough (baretile/runtime.py:791-812); a new arena from the driver when none is."""
+    self.check()
+    size = max(ALIGN, -(-size // ALIGN) * ALIGN)
+    for attempt in range(2):
+      for i, (addr, room) in enumerate(self.holes):
+        if room >= size:
+          self.holes[i:i + 1] = [(addr + size, room - size)] if room > size else []
+          self.used[addr] = size
+          return addr
+      if attempt: break
+      arena, addr = max(size, ARENA), ctypes.c_uint64()
+      try: _lib.call("bt_malloc", self.device, arena, ctypes.byref(addr))
+      except MemoryError: raise MemoryError(f"no {size} bytes free in DRAM") from None
+      self.arenas.append((addr.value, arena))
+      self.holes.append((addr.value, arena))
+    raise MemoryError(f"no {size} bytes free in DRAM")
+
+  def dram_free(self, addr):
+    """Release an allocation (baretile/runtime.py:814-820). Work already queued may still use it; work queued
+    later may reuse it, which the stream's ordering makes safe."""
+    if not self.active: return
+    size = self.used.pop(addr, None)
+    if size is None: return
+    self.holes.append((addr, size))
+    _merge_holes(self.holes)
+
+  def record(self): return Recording(self)
+
+  # ---- host <-> device ----
+  def host_alloc(self, size):
+    """Page-locked host memory as a ctypes byte array: the reference's host DMA page (baretile/runtime.py:548-600).
+    Copies from and to it are asynchronous."""
+    ptr = ctypes.c_void_p()
+    _lib.call("bt_host_alloc", size, ctypes.byref(ptr))
+    buf = (ctypes.c_char * size).from_address(ptr.value)
+    self.pinned = getattr(self, "pinned", [])
+    self.pinned.append(ptr.value)
+    return buf
+
+  def upload_async(self, addr, buf, n=None):
+    """Queue a copy from page-locked host memory to device memory; returns at once."""
+    self.check()
+    _lib.call("bt_h2d", self.device, addr, ctypes.addressof(buf), len(buf) if n is None else n, self.stream)
+
+  def download_async(self, buf, addr, n=None):
+    """Queue a copy from device memory into page-locked host memory; wait() before reading it."""
+    self.check()
+    _lib.call("bt_d2h", self.device, ctypes.addressof(buf), addr, len(buf) if n is None else n, self.stream)
+
+  def upload(self, addr, data):
+    """Copy host bytes to device memory at addr, in order with the queued launches."""
+    self.check()
+    data = bytes(data) if not isinstance(data, (bytes, bytearray)) else data
+    buf = (ctypes.c_char * len(data)).from_buffer_copy(data)
+    _lib.call("bt_h2d", self.device, addr, ctypes.cast(buf, ctypes.c_void_p), len(data), self.stream)
+    _lib.call("bt_stream_sync", self.device, self.stream, -1)   # buf is pageable and short-lived
+
+  def download(self, addr, n):
+    """n bytes of device memory at addr, after the queued launches."""
+    self.check()
+    buf = ctypes.create_string_buffer(n)
+    _lib.call("bt_d2h", self.device, ctypes.cast(buf, ctypes.c_void_p), addr, n, self.stream)
+    _lib.call("bt_stream_sync", self.device, self.stream, -1)
+    return buf.raw

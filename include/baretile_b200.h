@@ -1,0 +1,130 @@
+/* C-ABI of libbaretile_b200.so: the B200 backend for baretile's block-float matmul path.
+ *
+ * The reference reaches its device through a ctypes-loaded C library with explicit argtypes
+ * (baretile/pci.py:52-63: libttsim_init, libttsim_pci_mem_rd_bytes/wr_bytes, libttsim_clock). This
+ * header is the matching boundary for a CUDA device: plain pointers and sizes, no C++ or torch types.
+ * Each entry point names the reference interface it stands in for (paths inside the baretile project).
+ *
+ * Conventions
+ *   - Every function returns a status: BT_OK, or an error whose text bt_last_error() gives.
+ *     Host code maps BT_BAD_ARGUMENT -> ValueError, BT_DEVICE -> RuntimeError, BT_TIMEOUT -> TimeoutError,
+ *     BT_NO_MEMORY -> MemoryError, as the reference raises them (docs/api.md:51-62).
+ *   - Device addresses and stream/event handles travel as uint64_t.
+ *   - Work is queued on the given stream and runs in order, asynchronously, like launches on the
+ *     reference's command ring (baretile/runtime.py:680-771). bt_stream_sync waits.
+ *   - The library never frees or allocates device memory behind the caller's back: only
+ *     bt_malloc / bt_free do.
+ *   - Tensors are in tile layout: 32x32 tiles in row order, each tile four row-major 16x16 faces
+ *     (baretile/tensix.py:6-9). A bfp tile is 64 exponent bytes followed by its values
+ *     (baretile/tensix.py:14-20): 1088 bytes for bfp8, 576 for bfp4.
+ */
+#ifndef BARETILE_B200_H
+#define BARETILE_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { BT_OK = 0, BT_BAD_ARGUMENT = 1, BT_DEVICE = 2, BT_TIMEOUT = 3, BT_NO_MEMORY = 4 };
+enum { BT_BF16 = 0, BT_FP32 = 1, BT_INT32 = 2, BT_BFP8 = 8, BT_BFP4 = 4 };            /* storage formats */
+enum { BT_EPI_NONE = 0, BT_EPI_RELU = 1, BT_EPI_SILU = 2, BT_EPI_GLU = 3, BT_EPI_ARGMAX = 4 };
+
+typedef struct bt_device_info {
+  char name[64];
+  int sm_count, cc_major, cc_minor, l2_bytes;
+  uint64_t memory_bytes;
+  int max_shared_bytes, clock_khz;
+} bt_device_info;
+
+/* Text of the calling thread's last error. */
+const char *bt_last_error(void);
+
+/* ---- device, memory, streams, events: stand in for pci.open_device / Chip / Runtime
+ *      (baretile/pci.py:453-463, baretile/chip.py:75-83, baretile/runtime.py:543-923) ---- */
+int bt_device_count(int *count);                       /* pci.Sim.chips / find_cards */
+int bt_device_info_get(int device, bt_device_info *out); /* Chip telemetry (chip.py:22-31) */
+int bt_malloc(int device, size_t bytes, uint64_t *ptr);  /* the DRAM a Runtime carves (runtime.py:791-812) */
+int bt_free(int device, uint64_t ptr);
+int bt_host_alloc(size_t bytes, void **ptr);           /* the runtime's host DMA page (runtime.py:548-600) */
+int bt_host_free(void *ptr);
+int bt_stream_create(int device, uint64_t *stream);    /* the command ring */
+int bt_stream_destroy(int device, uint64_t stream);
+int bt_stream_sync(int device, uint64_t stream, int timeout_ms); /* Runtime.wait(timeout) (runtime.py:858-880) */
+int bt_stream_query(int device, uint64_t stream, int *done);     /* Runtime.finished (runtime.py:837) */
+int bt_h2d(int device, uint64_t dst, const void *src, size_t bytes, uint64_t stream); /* Chip.write / upload_kernel */
+int bt_d2h(int device, void *dst, uint64_t src, size_t bytes, uint64_t stream);       /* Chip.read / readback_kernel */
+int bt_d2d(int device, uint64_t dst, uint64_t src, size_t bytes, uint64_t stream);    /* copy_kernel (kernels.py:1051) */
+int bt_memset(int device, uint64_t dst, int value, size_t bytes, uint64_t stream);    /* zeros_kernel (kernels.py:1439) */
+int bt_event_create(int device, uint64_t *event);      /* dispatcher timestamps (runtime.py:773-786) */
+int bt_event_destroy(int device, uint64_t event);
+int bt_event_record(int device, uint64_t event, uint64_t stream);
+int bt_event_elapsed_ms(int device, uint64_t start, uint64_t end, float *ms);
+
+/* ---- replay: tensor.jit / Recording (baretile/tensor.py:1171-1293, baretile/runtime.py:725-732) ----
+ * Between bt_graph_begin and bt_graph_end the launches queued on the stream are recorded instead of run;
+ * bt_graph_launch replays the recording with one call, as the reference replays a block of commands with one
+ * doorbell write. Recorded launches keep the addresses they were queued with. */
+int bt_graph_begin(int device, uint64_t stream);
+int bt_graph_end(int device, uint64_t stream, uint64_t *graph);
+int bt_graph_launch(int device, uint64_t graph, uint64_t stream);
+int bt_graph_destroy(int device, uint64_t graph);
+
+/* ---- layout: Tensor.frombytes / Tensor.tobytes (baretile/tensor.py:107-135, :159-193) ----
+ * Row-major (batch, rows, cols) of itemsize-byte values <-> tiles. Padding is zero; a dimension of
+ * size 1 repeats across its tile. itemsize is 2 or 4. */
+int bt_tilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, int rows, int cols, uint64_t stream);
+int bt_untilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, int rows, int cols, uint64_t stream);
+/* fp32 -> bf16, round to nearest even, NaN kept quiet: tensix.round_bf16 (baretile/tensix.py:240-242). */
+int bt_round_bf16(int device, uint64_t src_f32, uint64_t dst_bf16, size_t count, uint64_t stream);
+
+/* ---- block-float pack / unpack ----
+ * bt_pack_bfp: Tensor.cast("bfp8" | "bfp4") (baretile/tensor.py:581-596): the packer's bfp8 rounding
+ * (baretile/kernels.py:1108-1114, baretile/models/gpt2.py:19-30) and bfp4_kernel
+ * (baretile/kernels.py:1074-1081, :1527-1567). src: ntiles bf16 tiles; dst: ntiles bfp tiles.
+ * bt_unpack_bfp: the unpacker's conversion, storage_kernel (baretile/kernels.py:1483-1525) and
+ * tensor._bf16s (baretile/tensor.py:1095-1104). */
+int bt_pack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, uint64_t stream);
+int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, uint64_t stream);
+
+/* Tensor.columns() / columns_kernel (baretile/tensor.py:598-611, baretile/kernels.py:1455-1481): a pure
+ * byte permutation of a (tile_rows x tile_cols) block-float matrix into the layout the matmul streams.
+ * Runs of 16 tile columns; inside a run, tile row by tile row; inside a tile, exponents then values,
+ * both ordered for one 128-bit load per lane. to_stream = 0 undoes it. */
+int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols, uint64_t src, uint64_t dst,
+                uint64_t stream);
+
+/* ---- the matmul: fused_kernel's decode paths (baretile/kernels.py:216-253, :543-584) ----
+ * out[M, N] = epilogue(alpha * (x[M, K] @ W[K, N]) + add), M <= 32.
+ *   x      bf16 tiles, one tile row (K/32 tiles).  K and N are multiples of 32.
+ *   w, w2  block-float weights in streaming layout (bt_relayout). w2 only for BT_EPI_GLU:
+ *          out = silu(x @ w) * (x @ w2) (baretile/models/llama.py:179-183).
+ *   add    0, or bf16 tiles of an (M or 1) x N addend, added before the activation
+ *          (baretile/kernels.py:593-599).
+ *   out    bf16 or fp32 tiles (out_dtype), rows past M zero; or with BT_EPI_ARGMAX nothing, and
+ *          arg_val[M] (fp32) / arg_idx[M] (int32) receive each row's largest value and its first
+ *          column (topk_kernel's tie rule, baretile/kernels.py:1173-1231), index + arg_base.
+ *   work   scratch of at least bt_gemv_workspace_bytes() bytes, zeroed once before first use;
+ *          launches that share it must not overlap.
+ * Products are exact, sums are fp32, outputs round half up to bf16 like the packer
+ * (docs/compiler.md, "Matmul precision"). */
+int bt_gemv_workspace_bytes(int device, size_t *bytes);
+int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
+                uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx,
+                int arg_base, uint64_t work, size_t work_bytes, uint64_t stream);
+/* Nonzero in *error once a bounded wait inside a launch that used this scratch gave up (its results are then
+ * unreliable): the counterpart of Runtime.wait's timeout report (baretile/runtime.py:866-876). Synchronises the
+ * stream, and clears the flag. */
+int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error);
+/* Tuning knobs (the reference's module constants tensix.DEPTH / CHUNKS, baretile/tensix.py:716-722): tile columns
+ * per sub-panel (4, 8 or 16) for up to 8, 16 and 32 rows of x, and pipeline stages (0: as many as fit). A 0 for a
+ * width keeps the current setting. */
+int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages);
+/* Number of GPU kernels this library has launched on behalf of the calling process. */
+int bt_launch_count(uint64_t *count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,87 @@
+"""The C-ABI boundary and the host-side mirror, without a GPU: the library loads and exports every symbol the header
+declares, the Python bindings agree with the header, and argument checks run before anything touches a device."""
+import ctypes, pathlib, re, subprocess, sys
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "baretile_b200.h").read_text()
+
+
+def declared():
+  code = re.sub(r"/\*.*?\*/", "", HEADER, flags=re.S)
+  return {m.group(2): m.group(3) for m in re.finditer(r"\b(int|const char \*)\s*(bt_\w+)\s*\(([^;]*)\)\s*;", code)}
+
+
+@pytest.fixture(scope="module")
+def built():
+  so = ROOT / "baretile_b200" / "libbaretile_b200.so"
+  if not so.exists():
+    run = subprocess.run(["make", "-C", str(ROOT / "baretile_b200" / "csrc"), "-j4"], capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr[-2000:]
+  return so
+
+
+def test_library_exports_every_declared_symbol(built):
+  lib, names = ctypes.CDLL(str(built)), declared()
+  assert len(names) >= 25
+  for name in names: assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_bindings_match_header(built):
+  from baretile_b200 import _lib
+  names = declared()
+  for name, argtypes in _lib.SIGNATURES.items():
+    assert name in names, f"{name} is bound but not declared"
+    params = [p for p in names[name].split(",") if p.strip() and p.strip() != "void"]
+    assert len(params) == len(argtypes), (name, names[name])
+  assert set(names) - set(_lib.SIGNATURES) == {"bt_last_error"}
+  _lib.lib()
+
+
+def test_argument_checks_need_no_device(built):
+  from baretile_b200 import _lib
+  n = ctypes.c_int(-1)
+  _lib.call("bt_device_count", ctypes.byref(n))
+  assert n.value >= 0
+  with pytest.raises(ValueError, match="bfp8"): _lib.call("bt_pack_bfp", 0, 3, 256, 512, 1, 0)
+  with pytest.raises(ValueError, match="1 to 32 rows"): _lib.call("bt_gemv_bfp", 0, 8, 0, 40, 64, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, 256, 1 << 30, 0)
+  with pytest.raises(ValueError, match="multiples of 32"): _lib.call("bt_gemv_bfp", 0, 8, 0, 8, 60, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, 256, 1 << 30, 0)
+  with pytest.raises(ValueError, match="GLU"): _lib.call("bt_gemv_bfp", 0, 8, 3, 8, 64, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, 256, 1 << 30, 0)
+  with pytest.raises(ValueError, match="sub-panel width"): _lib.call("bt_gemv_tune", 5, 0, 0, 0)
+  assert b"sub-panel" in _lib.lib().bt_last_error()
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+  from baretile_b200 import _lib
+  monkeypatch.setattr(_lib, "_lib", None)
+  monkeypatch.setattr(_lib, "PATH", tmp_path / "libbaretile_b200.so")
+  with pytest.raises(RuntimeError, match="no CPU fallback"): _lib.lib()
+
+
+def test_tensor_checks_without_a_device():
+  # bad calls raise ValueError before any allocation, also under python -O (reference: test/test_kernels.py:370-389)
+  code = """
+from baretile_b200.tensor import Tensor
+class Runtime:
+  def check(self): pass
+  def dram_alloc(self, size): return 0
+  def dram_free(self, addr): pass
+rt = Runtime()
+x, y = Tensor(rt, 2, 3), Tensor(rt, 2, 3)
+for bad in (lambda: x @ y, lambda: x + Tensor(rt, 3, 2), lambda: Tensor.frombytes(rt, 1, 1, bytes(2), dtype="bfp8"),
+            lambda: Tensor(rt, 0, 1), lambda: Tensor(rt, 1, 1, dtype="float64"), lambda: Tensor.of(rt, [[1, 2], [3]]),
+            lambda: x.cast("int32") @ y, lambda: x.columns(), lambda: x.topk(1)):
+  try: bad()
+  except ValueError: continue
+  raise SystemExit("no ValueError")
+print("all raised")
+"""
+  run = subprocess.run([sys.executable, "-O", "-c", code], capture_output=True, text=True, timeout=120, cwd=ROOT)
+  assert run.returncode == 0 and run.stdout.strip() == "all raised", run.stdout + run.stderr
+
+
+def test_hole_allocator_merges():
+  from baretile_b200.runtime import _merge_holes
+  holes = [(512, 256), (0, 256), (256, 256), (2048, 64)]
+  _merge_holes(holes)
+  assert holes == [(0, 768), (2048, 64)]
