@@ -5,13 +5,14 @@
 //
 // Decomposition ("stream-K"). The weight matrix is cut into sub-panels of WC tile columns. A unit is one tile
 // row of one sub-panel (WC tiles). Units are numbered sub-panel by sub-panel and dealt out in equal contiguous
-// ranges to one persistent CTA per SM, so every SM streams the same number of bytes whatever the shape. A CTA
-// whose range ends inside a sub-panel writes its fp32 partial sums to scratch; the last CTA to arrive at that
-// sub-panel (an atomic counter tells it) adds the partials in CTA order, so results do not depend on timing,
-// and runs the epilogue.
+// ranges to one persistent CTA per SM, so every SM streams the same number of bytes whatever the shape. A
+// sub-panel that several CTAs share is finished by the CTA that holds its last tile row: the others write their
+// fp32 partial sums to scratch and bump a counter; the owner, which takes that sub-panel last, waits for the
+// counter (with a limit), adds the partials in CTA order, so results do not depend on timing, and runs the
+// epilogue. The launch is cooperative, so all CTAs are resident and the wait cannot starve.
 //
-// Inside a CTA: warp 16 is the producer. One of its lanes waits for a free stage, announces the stage's bytes
-// to the stage's mbarrier and issues the bulk copies (weights and the matching tiles of x). The 16 consumer
+// Inside a CTA: warp 16 is the producer. One of its lanes waits for a free stage and announces the stage's bytes
+// to the stage's mbarrier; then each lane issues one bulk copy (a run of weights, or a piece of an x tile). The 16 consumer
 // warps form a WC x KS grid: warp (ck, cc) takes column cc of the sub-panel and every KS-th tile row of the
 // stage, so x tiles in shared memory serve WC warps. A weight tile is four 16x16 faces; a face is one
 // m16n8k16 MMA with the face's 16 output channels as the MMA's rows, 16 input channels as its K and up to 8
@@ -21,17 +22,18 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "stream_layout.cuh"
+#include "tmap.cuh"
+#include <cstring>
 
 using namespace bt;
 
 namespace {
 
 constexpr int kConsumerWarps = 16;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kMaxCtas = 256;
 constexpr int kMaxSubPanels = 16384;
-constexpr uint32_t kSpinLimit = 1u << 21;
+constexpr uint32_t kSpinLimit = 1u << 14;   // attempts of up to 100 us each (mbarriers) or 64 ns polls x 32 (counters)
 constexpr int kSmemBudget = 225 * 1024;
 
 // Scratch layout (byte offsets into the caller's workspace).
@@ -42,7 +44,7 @@ constexpr size_t kWsArgVal = kWsCounters + 4 * kMaxSubPanels;    // float[kMaxSu
 constexpr size_t kWsArgIdx = kWsArgVal + 4 * 32 * kMaxSubPanels; // int[kMaxSubPanels][32]
 constexpr size_t kWsPartials = kWsArgIdx + 4 * 32 * kMaxSubPanels;
 constexpr size_t kSlotFloatsMax = 2 * 16 * 2 * 4 * 4 * 32;       // NW * WC * 2 * TG * 4 * 32 at its largest
-constexpr size_t kWsBytes = kWsPartials + (size_t)kMaxCtas * 2 * kSlotFloatsMax * 4;
+constexpr size_t kWsBytes = kWsPartials + (size_t)kMaxCtas * kSlotFloatsMax * 4;
 
 struct GemvParams {
   const uint8_t *x;
@@ -51,14 +53,22 @@ struct GemvParams {
   void *out;
   float *arg_val;
   int *arg_idx;
-  uint8_t *work;
+  // scratch, zero before first use: a wait-gave-up flag, sub-panels finished (argmax), CTAs arrived per sub-panel,
+  // per-sub-panel argmax candidates, and one slot of partial sums per CTA
+  int *error, *panels_done, *counters, *part_idx;
+  float *part_val, *partials;
   float alpha;
   int arg_base, M, KT, TC, epi, out_fp32, nstages;
+  unsigned long long *trace;  // when set: 8 timestamps per CTA (debugging aid)
 };
 
 template <int FMT, int NW, int TG, int WC>
 struct Config {
-  static constexpr int KS = kConsumerWarps / WC;                 // k-slices: warps sharing a column
+  // Consumer warps. 16, except for the widest accumulators (32 rows of a gate/up pair), where 12 warps leave each
+  // thread 128 registers instead of 96.
+  static constexpr int CW = WC == 12 ? 12 : 16;
+  static constexpr int THREADS = (CW + 1) * 32;
+  static constexpr int KS = CW / WC;                             // k-slices: warps sharing a column
   static constexpr int T = NW == 2 ? 1 : 2;                      // tile rows a warp takes per stage
   static constexpr int UPS = KS * T;                             // units (tile rows) per stage
   static constexpr int TB = tile_bytes(FMT);
@@ -66,10 +76,23 @@ struct Config {
   static constexpr int W_BYTES = UPS * NW * WC * TB;
   static constexpr int STAGE = (W_BYTES + UPS * XB + 127) / 128 * 128;
   static constexpr int ACC = NW * 2 * TG * 4;                    // accumulator floats per lane
-  static constexpr int RED = KS > 1 ? WC * ACC * 32 * 4 : 0;     // cross-warp reduction buffer
+  static constexpr int SLAB = WC * ACC * 32 * 4;                 // one k-slice's accumulators, all columns
+  static constexpr int RED_SLABS = KS > 1 ? (24576 / SLAB < 1 ? 1 : 24576 / SLAB < KS - 1 ? 24576 / SLAB : KS - 1) : 0;
+  static constexpr int RED = RED_SLABS * SLAB;                   // cross-warp reduction buffer
   static constexpr int FIXED = 4352 + RED;                       // barriers, flags, argmax staging, reduction buffer
   static constexpr size_t SLOT = (size_t)WC * ACC * 32;          // floats in one partial slot
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#ifdef BT_GEMV_TRACE
+#define BT_TRACE(slot, cond) do { if (p.trace && (cond)) p.trace[blockIdx.x * 8 + (slot)] = global_ns(); } while (0)
+#else
+#define BT_TRACE(slot, cond) do { } while (0)
+#endif
 
 __device__ __forceinline__ long long range_start(long long units, int b, int ctas) { return units * b / ctas; }
 __device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
@@ -85,37 +108,40 @@ __device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
   return prmt(ew, 0u, HI ? 0x4342u : 0x4140u) * 128u + 0x1F801F80u;
 }
 
-// One weight tile times the staged x tile, added into acc[ng][tg][4].
+// One weight tile times the staged x tile, added into acc[ng][tg][4]. `tile` and `xs` are shared-memory addresses
+// that already include the lane's own offsets: tile = tile base + 16 * lane; xs = x tile base + 32 * g + 8 * t
+// (g = lane / 4, t = lane % 4); `ex` = tile base + 16 * t, where the lane's exponents are.
 template <int FMT, int TG>
-__device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t xs, int lane, float (&acc)[2][TG][4]) {
-  const int g = lane >> 2, t = lane & 3;
-  const uint4 ev = lds128(tile + t * 16);
+__device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t ex, uint32_t xs, float (&acc)[2][TG][4]) {
+  const uint4 ev = lds128(ex);
   const uint32_t ee[4] = {ev.x, ev.y, ev.z, ev.w};
-  uint4 wq = make_uint4(0, 0, 0, 0);
-  if (FMT == BT_BFP4) wq = lds128(tile + 64 + lane * 16);
+  uint4 wv[2];
+  if (FMT == BT_BFP8) wv[0] = lds128(tile + 64), wv[1] = lds128(tile + 64 + 512);
+  else wv[0] = lds128(tile + 64), wv[1] = wv[0];
+  uint2 bx[2][TG];
 #pragma unroll
   for (int h = 0; h < 2; h++) {
-    uint4 wv = make_uint4(0, 0, 0, 0);
-    if (FMT == BT_BFP8) wv = lds128(tile + 64 + h * 512 + lane * 16);
-    uint2 bx[TG];
 #pragma unroll
-    for (int tg = 0; tg < TG; tg++) bx[tg] = lds64(xs + (TG == 1 ? h * 256 + g * 32 : (tg >> 1) * 1024 + h * 512 + ((tg & 1) * 8 + g) * 32) + t * 8);
+    for (int tg = 0; tg < TG; tg++) bx[h][tg] = lds64(xs + (TG == 1 ? h * 256 : (tg >> 1) * 1024 + h * 512 + (tg & 1) * 256));
+  }
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
 #pragma unroll
     for (int fs = 0; fs < 2; fs++) {
       const uint32_t ew = ee[2 * h + fs];
       const uint32_t s01 = scale_pair<0>(ew), s23 = scale_pair<1>(ew);
       uint32_t m0, s0, m1, s1;  // magnitude and sign bytes of MMA rows g (channel 2g) and g + 8 (channel 2g + 1)
       if (FMT == BT_BFP8) {
-        const uint32_t w0 = fs ? wv.z : wv.x, w1 = fs ? wv.w : wv.y;
+        const uint32_t w0 = fs ? wv[h].z : wv[h].x, w1 = fs ? wv[h].w : wv[h].y;
         m0 = w0 & 0x7F7F7F7Fu, s0 = w0 & 0x80808080u, m1 = w1 & 0x7F7F7F7Fu, s1 = w1 & 0x80808080u;
       } else {
-        const uint32_t wb = h ? (fs ? wq.w : wq.z) : (fs ? wq.y : wq.x), wl = wb << 4;
+        const uint32_t wb = h ? (fs ? wv[0].w : wv[0].z) : (fs ? wv[0].y : wv[0].x), wl = wb << 4;
         m0 = wl & 0x70707070u, s0 = wl & 0x80808080u, m1 = wb & 0x70707070u, s1 = wb & 0x80808080u;
       }
       const uint32_t a0 = mul_bf16x2(prmt(m0, s0, 0x5140u), s01), a1 = mul_bf16x2(prmt(m1, s1, 0x5140u), s01);
       const uint32_t a2 = mul_bf16x2(prmt(m0, s0, 0x7362u), s23), a3 = mul_bf16x2(prmt(m1, s1, 0x7362u), s23);
 #pragma unroll
-      for (int tg = 0; tg < TG; tg++) mma_bf16(acc[fs][tg], a0, a1, a2, a3, bx[tg].x, bx[tg].y);
+      for (int tg = 0; tg < TG; tg++) mma_bf16(acc[fs][tg], a0, a1, a2, a3, bx[h][tg].x, bx[h][tg].y);
     }
   }
 }
@@ -191,8 +217,32 @@ __device__ __forceinline__ void finish_column(const GemvParams &p, const float (
   }
 }
 
+// The unit ranges of a CTA in the order it takes them. A sub-panel that several CTAs share is finished by the CTA
+// that holds its last tile row (its owner); the others hand it their partial sums through global memory. So a CTA
+// first takes the sub-panel its range ends in (it is that one's first contributor, and the owner will not need the
+// sums for a while), then the sub-panels it has whole, and last the sub-panel its range starts in, which it owns:
+// by then the other contributors have long signalled, or are finishing at the same moment.
+struct Segments {
+  long long a[3], b[3];
+  int n;
+};
+__device__ __forceinline__ Segments segments_of(long long u0, long long u1, int KT) {
+  Segments s;
+  s.n = 0;
+  if (u0 >= u1) return s;
+  const long long head_end = min(u1, (u0 / KT + 1) * KT);            // end of the sub-panel the range starts in
+  const bool head_partial = u0 % KT != 0 || head_end - u0 < KT;
+  const long long tail_start = (u1 / KT) * KT;                       // start of the sub-panel the range ends in
+  const bool tail_partial = u1 % KT != 0 && tail_start >= head_end;  // a tail that is not the head itself
+  long long mid_a = head_partial ? head_end : u0, mid_b = tail_partial ? tail_start : u1;
+  if (tail_partial) s.a[s.n] = tail_start, s.b[s.n++] = u1;
+  if (mid_b > mid_a) s.a[s.n] = mid_a, s.b[s.n++] = mid_b;
+  if (head_partial) s.a[s.n] = u0, s.b[s.n++] = head_end;
+  return s;
+}
+
 template <int FMT, int NW, int TG, int WC>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap xmap) {
   using C = Config<FMT, NW, TG, WC>;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -201,166 +251,221 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
   float *arg_v = reinterpret_cast<float *>(smem + 256);           // [16][32] best value per column warp and token
   int *arg_i = reinterpret_cast<int *>(smem + 256 + 2048);        // [16][32] and its channel
   float *red = reinterpret_cast<float *>(smem + 4352);
-  const uint32_t stages = sbase + (C::FIXED + 127) / 128 * 128;
+  constexpr int kStageBase = (C::FIXED + 127) / 128 * 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ctas = gridDim.x, cta = blockIdx.x, KT = p.KT;
   const int subpanels = (p.TC + WC - 1) / WC;
   const long long units = (long long)subpanels * KT;
   const long long u0 = range_start(units, cta, ctas), u1 = range_start(units, cta + 1, ctas);
-  int *error = reinterpret_cast<int *>(p.work + kWsError);
+  const Segments seg = segments_of(u0, u1, KT);
+  int *error = p.error;
 
+  BT_TRACE(0, threadIdx.x == 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.nstages; s++) {
       mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, kConsumerWarps);
+      mbar_init(empty0 + 8 * s, C::CW);
     }
     mbar_fence_init();
   }
   __syncthreads();
+  BT_TRACE(1, threadIdx.x == 0);
 
-  if (warp == kConsumerWarps) {
-    // ---- producer ----
-    if (lane == 0) {
-      int it = 0;
-      for (long long u = u0; u < u1; it++) {
-        const int sp = (int)(u / KT), kt = (int)(u % KT);
-        const int n = (int)min((long long)C::UPS, min(u1 - u, (long long)(KT - kt)));
-        const int s = it % p.nstages;
-        if (it >= p.nstages && !mbar_wait(empty0 + 8 * s, (it / p.nstages - 1) & 1, kSpinLimit)) atomicExch(error, 1);
-        const int col0 = sp * WC, wcols = min(WC, p.TC - col0);
-        const int run = col0 / kPanel, width = min(kPanel, p.TC - run * kPanel);
-        const uint32_t bar = full0 + 8 * s, stage = stages + s * C::STAGE;
-        mbar_expect_tx(bar, n * (NW * wcols * C::TB + C::XB));
-        for (int i = 0; i < n; i++) {
-          const size_t tile = (size_t)run * kPanel * KT + (size_t)(kt + i) * width + col0 % kPanel;
-#pragma unroll
-          for (int m = 0; m < NW; m++) bulk_g2s(stage + (i * NW + m) * WC * C::TB, p.w[m] + tile * C::TB, wcols * C::TB, bar);
-          const uint8_t *xt = p.x + (size_t)(kt + i) * 2048;
-          const uint32_t xs = stage + C::W_BYTES + i * C::XB;
-          if (TG == 1) bulk_g2s(xs, xt, 256, bar), bulk_g2s(xs + 256, xt + 512, 256, bar);  // rows 0-7 of faces 0 and 1
-          else bulk_g2s(xs, xt, C::XB, bar);
+  if (warp == C::CW) {
+    // ---- producer: lane 0 waits for the stage to be free and announces its bytes; then one lane per copy issues it.
+    // A bulk copy costs the issuing warp on the order of a hundred cycles whatever its size, so a stage is a few
+    // large copies: one per run of weights, and one for the stage's x tiles (a tiled TMA box that picks the rows
+    // the MMAs need out of each tile, or for 32 rows the tiles as they are).
+    constexpr int RPS = WC / kPanel;             // runs of the streamed layout in a sub-panel
+    int s = 0;                 // the stage to fill next
+    uint32_t round = 0;        // how many times the ring has wrapped
+    for (int q = 0; q < seg.n; q++) {
+      int sp = (int)(seg.a[q] / KT), kt = (int)(seg.a[q] % KT);
+      for (int left = (int)(seg.b[q] - seg.a[q]); left > 0;) {
+        const int n = min(min(C::UPS, left), KT - kt);
+        const uint32_t bar = full0 + 8 * s, stage = sbase + kStageBase + s * C::STAGE;
+        if (lane == 0) {
+          if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, kSpinLimit)) atomicExch(error, 1);
+          mbar_expect_tx(bar, n * NW * min(WC, p.TC - sp * WC) * C::TB + (TG == 4 ? n : C::UPS) * C::XB);
         }
-        u += n;
+        __syncwarp();
+        if (lane < NW * RPS) {
+          const int m = lane / RPS, r = lane % RPS, run = sp * RPS + r, width = min(kPanel, p.TC - run * kPanel);
+          if (width > 0)
+            bulk_g2s(stage + (m * RPS + r) * C::UPS * kPanel * C::TB, p.w[m] + ((size_t)run * kPanel * KT + (size_t)kt * width) * C::TB,
+                     n * width * C::TB, bar);
+        } else if (lane == NW * RPS) {
+          if (TG == 4) bulk_g2s(stage + C::W_BYTES, p.x + (size_t)kt * 2048, n * 2048, bar);
+          else tma_load_3d(stage + C::W_BYTES, &xmap, 0, 0, kt, bar);   // tiles past the last read as zeros
+        }
+        left -= n, kt += n;
+        if (kt == KT) kt = 0, sp++;
+        if (++s == p.nstages) s = 0, round++;
       }
     }
+    BT_TRACE(5, lane == 0);
     return;
   }
 
   // ---- consumers ----
-  const int ck = warp / WC, cc = warp % WC, g = lane >> 2, t = lane & 3;
+  const int ck = warp / WC, cc = warp % WC;
+  constexpr int RPS = WC / kPanel;
+  const int warp_tile = ((cc / kPanel) * C::UPS * kPanel + cc % kPanel) * C::TB;   // this warp's column inside a stage
   float acc[NW][2][TG][4];
 // accumulator i of the lane, with i a compile-time constant after unrolling, so that acc stays in registers
 #define ACC_AT(i) acc[(i) / (8 * TG)][(i) / (4 * TG) % 2][(i) / 4 % TG][(i) % 4]
 #pragma unroll
   for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
 
-  int it = 0;
-  for (long long u = u0; u < u1; it++) {
-    const int sp = (int)(u / KT), kt = (int)(u % KT);
-    const int n = (int)min((long long)C::UPS, min(u1 - u, (long long)(KT - kt)));
-    const int s = it % p.nstages;
-    if (!mbar_wait(full0 + 8 * s, (it / p.nstages) & 1, kSpinLimit)) atomicExch(error, 2);
-    const uint32_t stage = stages + s * C::STAGE;
-    const int col = sp * WC + cc;
-    if (col < p.TC) {
-      for (int i = ck; i < n; i += C::KS) {
+  const int g = lane >> 2, tl = lane & 3;
+  // shared-memory addresses of this lane's pieces, relative to a stage: its 16 bytes of a tile's values, its exponents
+  // and its rows of an x tile
+  const uint32_t lane_tile = sbase + kStageBase + warp_tile + lane * 16, lane_ex = sbase + kStageBase + warp_tile + tl * 16;
+  const uint32_t lane_x = sbase + kStageBase + C::W_BYTES + g * 32 + tl * 8;
+  int s = 0;
+  uint32_t round = 0;
+  bool first_stage = true;
+  for (int q = 0; q < seg.n; q++) {
+    int sp = (int)(seg.a[q] / KT), kt = (int)(seg.a[q] % KT);
+    for (int left = (int)(seg.b[q] - seg.a[q]); left > 0;) {
+      const int n = min(min(C::UPS, left), KT - kt);
+      if (!mbar_wait(full0 + 8 * s, round & 1, kSpinLimit)) atomicExch(error, 2);
+      BT_TRACE(2, threadIdx.x == 0 && first_stage);
+      first_stage = false;
+      const int col = sp * WC + cc;
+      if (col < p.TC) {
+        const int width = min(kPanel, p.TC - (sp * RPS + cc / kPanel) * kPanel);   // tiles of a tile row in this run
+        const uint32_t so = s * C::STAGE + ck * width * C::TB, xo = s * C::STAGE + ck * C::XB;
 #pragma unroll
-        for (int m = 0; m < NW; m++) tile_mma<FMT, TG>(stage + ((i * NW + m) * WC + cc) * C::TB, stage + C::W_BYTES + i * C::XB, lane, acc[m]);
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty0 + 8 * s);
-    u += n;
-    if (u != u1 && u % KT != 0) continue;
-
-    // ---- this CTA is done with sub-panel sp: reduce over k-slices, combine with other CTAs, run the epilogue ----
-    if (C::KS > 1) {
-      for (int r = 1; r < C::KS; r++) {
-        if (ck == r) {
+        for (int j = 0; j < C::T; j++) {                        // this warp's tile rows of the stage: ck, ck + KS, ...
+          if (ck + j * C::KS < n) {
 #pragma unroll
-          for (int i = 0; i < C::ACC; i++) red[(cc * C::ACC + i) * 32 + lane] = ACC_AT(i);
-        }
-        named_barrier(1, kConsumerWarps * 32);
-        if (ck == 0) {
-#pragma unroll
-          for (int i = 0; i < C::ACC; i++) ACC_AT(i) += red[(cc * C::ACC + i) * 32 + lane];
-        }
-        named_barrier(1, kConsumerWarps * 32);
-      }
-    }
-    const int first = cta_of((long long)sp * KT, units, ctas), last = cta_of((long long)(sp + 1) * KT - 1, units, ctas);
-    bool finish = true;
-    if (first != last) {
-      float *partials = reinterpret_cast<float *>(p.work + kWsPartials);
-      int *counter = reinterpret_cast<int *>(p.work + kWsCounters) + sp;
-      const int mine = cta * 2 + (sp == (int)(u0 / KT) ? 0 : 1);
-      if (ck == 0) {
-        float4 *slot = reinterpret_cast<float4 *>(partials + (size_t)mine * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
-#pragma unroll
-        for (int i = 0; i < C::ACC / 4; i++)
-          slot[i * 32 + lane] = make_float4(ACC_AT(4 * i), ACC_AT(4 * i + 1), ACC_AT(4 * i + 2), ACC_AT(4 * i + 3));
-        __threadfence();
-      }
-      named_barrier(1, kConsumerWarps * 32);
-      if (threadIdx.x == 0) flags[0] = atomicAdd(counter, 1) == last - first;
-      named_barrier(1, kConsumerWarps * 32);
-      finish = flags[0] != 0;
-      if (finish) {
-        __threadfence();
-        if (ck == 0) {
-#pragma unroll
-          for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
-          for (int c = first; c <= last; c++) {  // always in CTA order: the sum does not depend on who arrived last
-            const int theirs = c * 2 + (sp == (int)(range_start(units, c, ctas) / KT) ? 0 : 1);
-            const float4 *slot = reinterpret_cast<const float4 *>(partials + (size_t)theirs * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
-#pragma unroll
-            for (int i = 0; i < C::ACC / 4; i++) {
-              const float4 v = __ldcg(slot + i * 32 + lane);
-              ACC_AT(4 * i) += v.x, ACC_AT(4 * i + 1) += v.y, ACC_AT(4 * i + 2) += v.z, ACC_AT(4 * i + 3) += v.w;
+            for (int m = 0; m < NW; m++) {
+              const uint32_t o = so + (m * RPS * C::UPS * kPanel + j * C::KS * width) * C::TB;
+              tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + xo + j * C::KS * C::XB, acc[m]);
             }
           }
         }
-        if (threadIdx.x == 0) *counter = 0;  // ready for the next launch
       }
-    }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+      if (++s == p.nstages) s = 0, round++;
+      left -= n, kt += n;
+      BT_TRACE(3, threadIdx.x == 0 && q == seg.n - 1 && left == 0);
+      if (left != 0 && kt != KT) continue;
+      const int done_sp = sp;
+      if (kt == KT) kt = 0, sp++;
 
-    if (finish && ck == 0 && col < p.TC) finish_column<NW, TG>(p, acc, col, cc, lane, arg_v, arg_i);
-    if (p.epi == BT_EPI_ARGMAX && finish) {
-      // the sub-panel's best per token, then, in the last sub-panel to finish, the best over all sub-panels in order
-      named_barrier(1, kConsumerWarps * 32);
-      float *part_v = reinterpret_cast<float *>(p.work + kWsArgVal);
-      int *part_i = reinterpret_cast<int *>(p.work + kWsArgIdx);
-      const int wcols = min(WC, p.TC - sp * WC);
-      if (warp == 0) {
-        float v = arg_v[lane];
-        int i = arg_i[lane];
-        for (int c = 1; c < wcols; c++)
-          if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
-        part_v[sp * 32 + lane] = v, part_i[sp * 32 + lane] = i;
-        __threadfence();
-      }
-      named_barrier(1, kConsumerWarps * 32);
-      int *done = reinterpret_cast<int *>(p.work + kWsPanelsDone);
-      if (threadIdx.x == 0) flags[1] = atomicAdd(done, 1) == subpanels - 1;
-      named_barrier(1, kConsumerWarps * 32);
-      if (flags[1]) {
-        __threadfence();
-        if (warp == 0 && lane < p.M) {
-          float v = -INFINITY;
-          int i = 0x7FFFFFFF;
-          for (int q = 0; q < subpanels; q++) {
-            const float ov = __ldcg(part_v + q * 32 + lane);
-            const int oi = __ldcg(part_i + q * 32 + lane);
-            if (beats(ov, oi, v, i)) v = ov, i = oi;
-          }
-          p.arg_val[lane] = v, p.arg_idx[lane] = i + p.arg_base;
-        }
-        if (threadIdx.x == 0) *done = 0;
-      }
-    }
+      // ---- this CTA is done with sub-panel sp: reduce over k-slices, combine with other CTAs, run the epilogue ----
+      if (C::KS > 1) {
+        for (int r0 = 1; r0 < C::KS; r0 += C::RED_SLABS) {       // as many k-slices at a time as the buffer holds
+          if (ck >= r0 && ck < r0 + C::RED_SLABS) {
 #pragma unroll
-    for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
+            for (int i = 0; i < C::ACC; i++) red[(((ck - r0) * WC + cc) * C::ACC + i) * 32 + lane] = ACC_AT(i);
+          }
+          named_barrier(1, C::CW * 32);
+          if (ck == 0) {
+            for (int r = r0; r < min(C::KS, r0 + C::RED_SLABS); r++) {
+#pragma unroll
+              for (int i = 0; i < C::ACC; i++) ACC_AT(i) += red[(((r - r0) * WC + cc) * C::ACC + i) * 32 + lane];
+            }
+          }
+          if (r0 + C::RED_SLABS < C::KS) named_barrier(1, C::CW * 32);
+        }
+      }
+      BT_TRACE(6, threadIdx.x == 0 && q == seg.n - 1 && left == 0);
+      const int first = cta_of((long long)done_sp * KT, units, ctas), last = cta_of((long long)(done_sp + 1) * KT - 1, units, ctas);
+      const bool finish = cta == last;        // the owner finishes the sub-panel; the others only contribute
+      if (first != last) {
+        float *partials = p.partials;
+        int *counter = p.counters + done_sp;
+        if (!finish) {
+          // a contributor has one shared sub-panel that it does not own, so one slot per CTA is enough
+          if (ck == 0) {
+            float4 *slot = reinterpret_cast<float4 *>(partials + (size_t)cta * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
+#pragma unroll
+            for (int i = 0; i < C::ACC / 4; i++)
+              slot[i * 32 + lane] = make_float4(ACC_AT(4 * i), ACC_AT(4 * i + 1), ACC_AT(4 * i + 2), ACC_AT(4 * i + 3));
+            __threadfence();
+          }
+          named_barrier(1, C::CW * 32);
+          if (threadIdx.x == 0) atomicAdd(counter, 1);
+        } else {
+          // wait, with a limit, until the last - first other contributors have signalled
+          if (threadIdx.x == 0) {
+            uint32_t spins = 0;
+            while (*reinterpret_cast<volatile int *>(counter) < last - first) {
+              if (++spins > kSpinLimit * 32) { atomicExch(error, 3); break; }
+              __nanosleep(64);
+            }
+            *counter = 0;                      // ready for the next launch
+          }
+          named_barrier(1, C::CW * 32);
+          if (ck == 0) {
+            __threadfence();
+            // this CTA's own sums first, then the others' in CTA order: the result does not depend on timing
+            constexpr int BATCH = C::ACC <= 16 ? 4 : C::ACC <= 32 ? 2 : 1;   // contributors whose loads are in flight together
+            for (int c0 = first; c0 < last; c0 += BATCH) {
+              float4 v[BATCH][C::ACC / 4];
+#pragma unroll
+              for (int j = 0; j < BATCH; j++) {
+                const float4 *slot = reinterpret_cast<const float4 *>(partials + (size_t)(c0 + j) * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
+#pragma unroll
+                for (int i = 0; i < C::ACC / 4; i++) v[j][i] = c0 + j < last ? __ldcg(slot + i * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int j = 0; j < BATCH; j++) {
+#pragma unroll
+                for (int i = 0; i < C::ACC / 4; i++)
+                  ACC_AT(4 * i) += v[j][i].x, ACC_AT(4 * i + 1) += v[j][i].y, ACC_AT(4 * i + 2) += v[j][i].z, ACC_AT(4 * i + 3) += v[j][i].w;
+              }
+            }
+          }
+        }
+      }
+
+      BT_TRACE(7, threadIdx.x == 0 && q == seg.n - 1 && left == 0);
+      if (finish && ck == 0 && col < p.TC) finish_column<NW, TG>(p, acc, col, cc, lane, arg_v, arg_i);
+      if (p.epi == BT_EPI_ARGMAX && finish) {
+        // the sub-panel's best per token, then, in the last sub-panel to finish, the best over all sub-panels in order
+        named_barrier(1, C::CW * 32);
+        float *part_v = p.part_val;
+        int *part_i = p.part_idx;
+        const int wcols = min(WC, p.TC - done_sp * WC);
+        if (warp == 0) {
+          float v = arg_v[lane];
+          int i = arg_i[lane];
+          for (int c = 1; c < wcols; c++)
+            if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
+          part_v[done_sp * 32 + lane] = v, part_i[done_sp * 32 + lane] = i;
+          __threadfence();
+        }
+        named_barrier(1, C::CW * 32);
+        int *done = p.panels_done;
+        if (threadIdx.x == 0) flags[1] = atomicAdd(done, 1) == subpanels - 1;
+        named_barrier(1, C::CW * 32);
+        if (flags[1]) {
+          __threadfence();
+          if (warp == 0 && lane < p.M) {
+            float v = -INFINITY;
+            int i = 0x7FFFFFFF;
+            for (int qq = 0; qq < subpanels; qq++) {
+              const float ov = __ldcg(part_v + qq * 32 + lane);
+              const int oi = __ldcg(part_i + qq * 32 + lane);
+              if (beats(ov, oi, v, i)) v = ov, i = oi;
+            }
+            p.arg_val[lane] = v, p.arg_idx[lane] = i + p.arg_base;
+          }
+          if (threadIdx.x == 0) *done = 0;
+        }
+      }
+      // the next sub-panel's reduction must not overwrite `red` or the flags while a slower warp still reads them
+      if (C::KS > 1 || p.epi == BT_EPI_ARGMAX) named_barrier(1, C::CW * 32);
+#pragma unroll
+      for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
+    }
   }
+  BT_TRACE(4, threadIdx.x == 0);
 #undef ACC_AT
 }
 
@@ -368,6 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
 
 int g_wc[3] = {4, 8, 16};  // tile columns per sub-panel for 1, 2 and 4 token groups
 int g_stages = 0;          // 0: as many as fit
+unsigned long long *g_trace = nullptr;
 
 template <int FMT, int NW, int TG, int WC>
 int launch(const GemvParams &base, int sms, cudaStream_t stream) {
@@ -386,15 +492,28 @@ int launch(const GemvParams &base, int sms, cudaStream_t stream) {
   }
   const long long units = (long long)((p.TC + WC - 1) / WC) * p.KT;
   const int ctas = (int)min((long long)min(sms, kMaxCtas), units);
-  gemv_kernel<FMT, NW, TG, WC><<<ctas, kThreads, smem, stream>>>(p);
+  // x as (8 TG rows x 32 bytes, 2 faces, K tiles): a box picks the rows the MMAs read out of UPS consecutive tiles
+  alignas(64) CUtensorMap xmap;
+  memset(&xmap, 0, sizeof xmap);
+  if (TG < 4) {
+    const uint64_t dims[3] = {(uint64_t)(64 * TG), 2, (uint64_t)p.KT}, strides[2] = {512, 2048};
+    const uint32_t box[3] = {(uint32_t)(64 * TG), 2, (uint32_t)C::UPS};
+    if (int st = make_tmap(&xmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return st;
+  }
+  void *args[2] = {&p, &xmap};
+  BT_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(gemv_kernel<FMT, NW, TG, WC>), dim3(ctas), dim3(C::THREADS), args, smem, stream));
   return launched("gemv_kernel");
 }
 
 template <int FMT, int NW, int TG>
 int launch_wc(const GemvParams &p, int wc, int sms, cudaStream_t stream) {
-  if (wc == 4) return launch<FMT, NW, TG, 4>(p, sms, stream);
-  if (wc == 8) return launch<FMT, NW, TG, 8>(p, sms, stream);
-  return launch<FMT, NW, TG, 16>(p, sms, stream);
+  if constexpr (NW == 2 && TG == 4) {
+    return launch<FMT, NW, TG, 12>(p, sms, stream);   // the widest accumulators: see Config::CW
+  } else {
+    if (wc == 4) return launch<FMT, NW, TG, 4>(p, sms, stream);
+    if (wc == 8) return launch<FMT, NW, TG, 8>(p, sms, stream);
+    return launch<FMT, NW, TG, 16>(p, sms, stream);
+  }
 }
 
 template <int FMT, int NW>
@@ -447,11 +566,21 @@ int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
   BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
   GemvParams p{};
   p.x = as_ptr<uint8_t>(x), p.w[0] = as_ptr<uint8_t>(w), p.w[1] = as_ptr<uint8_t>(w2), p.add = as_ptr<uint16_t>(add);
-  p.out = as_ptr<void>(out), p.arg_val = as_ptr<float>(arg_val), p.arg_idx = as_ptr<int>(arg_idx), p.work = as_ptr<uint8_t>(work);
+  p.out = as_ptr<void>(out), p.arg_val = as_ptr<float>(arg_val), p.arg_idx = as_ptr<int>(arg_idx);
+  p.error = as_ptr<int>(work + kWsError), p.panels_done = as_ptr<int>(work + kWsPanelsDone), p.counters = as_ptr<int>(work + kWsCounters);
+  p.part_val = as_ptr<float>(work + kWsArgVal), p.part_idx = as_ptr<int>(work + kWsArgIdx), p.partials = as_ptr<float>(work + kWsPartials);
+  p.trace = g_trace;
   p.alpha = alpha, p.arg_base = arg_base, p.M = M, p.KT = K / 32, p.TC = N / 32, p.epi = epilogue, p.out_fp32 = out_dtype == BT_FP32;
   cudaStream_t st = as_stream(stream);
   if (fmt == BT_BFP8) return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP8, 2>(p, sms, st) : launch_tg<BT_BFP8, 1>(p, sms, st);
   return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP4, 2>(p, sms, st) : launch_tg<BT_BFP4, 1>(p, sms, st);
+}
+
+// Debugging aid: when `buffer` is nonzero, every later launch writes 8 nanosecond timestamps per CTA into it (kernel
+// start, barriers ready, first stage arrived, last stage consumed, kernel end, last copy issued). 0 turns it off.
+int bt_gemv_trace(uint64_t buffer) {
+  g_trace = as_ptr<unsigned long long>(buffer);
+  return BT_OK;
 }
 
 // Nonzero once a bounded wait inside a launch that used this scratch gave up; the results of that launch are

@@ -19,7 +19,7 @@
 
 namespace bt {
 
-constexpr int kPanel = 16;  // tile columns in a run
+constexpr int kPanel = 4;  // tile columns in a run
 
 // Position in the streamed tile of canonical byte c.
 template <int FMT>

@@ -170,7 +170,7 @@ class Tensor:
     raise ValueError(f"this backend casts between bf16 and block floats, not {self.dtype} to {dtype}")
 
   def columns(self):
-    """Store the matrix the way matmul streams its B (baretile/tensor.py:598-611). Here: runs of 16 tile columns,
+    """Store the matrix the way matmul streams its B (baretile/tensor.py:598-611). Here: runs of 4 tile columns,
     tile row by tile row, each tile's bytes ordered for the kernel's loads. A pure permutation; it reads back as
     it was."""
     if self.dtype not in BFP:
@@ -178,7 +178,7 @@ class Tensor:
     if self.runs: return self
     x = self.realize()
     out = Tensor(self.rt, self.rows, self.cols, batch=self.batch, dtype=self.dtype)
-    out.runs = (-(-self.tc // 16), self.tr, 0)
+    out.runs = (-(-self.tc // 4), self.tr, 0)
     self._relayout(x.addr, out.addr, to_stream=1)
     return out
 

@@ -90,7 +90,7 @@ int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles
 
 /* Tensor.columns() / columns_kernel (baretile/tensor.py:598-611, baretile/kernels.py:1455-1481): a pure
  * byte permutation of a (tile_rows x tile_cols) block-float matrix into the layout the matmul streams.
- * Runs of 16 tile columns; inside a run, tile row by tile row; inside a tile, exponents then values,
+ * Runs of 4 tile columns; inside a run, tile row by tile row; inside a tile, exponents then values,
  * both ordered for one 128-bit load per lane. to_stream = 0 undoes it. */
 int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols, uint64_t src, uint64_t dst,
                 uint64_t stream);
@@ -121,6 +121,10 @@ int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error);
  * per sub-panel (4, 8 or 16) for up to 8, 16 and 32 rows of x, and pipeline stages (0: as many as fit). A 0 for a
  * width keeps the current setting. */
 int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages);
+/* Debugging aid (the reference's kernel print rings, baretile/runtime.py:882-901): with a nonzero device buffer of
+ * 32 KiB, every later matmul launch writes 8 nanosecond timestamps per CTA into it, and CTA 0 adds four cycle
+ * counts for each of its first 64 stages. 0 turns it off. */
+int bt_gemv_trace(uint64_t buffer);
 /* Number of GPU kernels this library has launched on behalf of the calling process. */
 int bt_launch_count(uint64_t *count);
 

@@ -145,7 +145,7 @@ def unpack_tiles(tiles, dtype):
 
 # ---- streaming layout (the B200 backend's own `columns()` permutation) -------------------------------
 
-PANEL = 16  # tile columns per run
+PANEL = 4  # tile columns per run
 
 
 def stream_perm(dtype):
