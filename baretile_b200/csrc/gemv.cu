@@ -517,10 +517,10 @@ int launch_wc(const GemvParams &p, int wc, int sms, cudaStream_t stream) {
 }
 
 template <int FMT, int NW>
-int launch_tg(const GemvParams &p, int sms, cudaStream_t stream) {
-  if (p.M <= 8) return launch_wc<FMT, NW, 1>(p, g_wc[0], sms, stream);
-  if (p.M <= 16) return launch_wc<FMT, NW, 2>(p, g_wc[1], sms, stream);
-  return launch_wc<FMT, NW, 4>(p, g_wc[2], sms, stream);
+int launch_tg(const GemvParams &p, int wc_force, int sms, cudaStream_t stream) {
+  if (p.M <= 8) return launch_wc<FMT, NW, 1>(p, wc_force ? wc_force : g_wc[0], sms, stream);
+  if (p.M <= 16) return launch_wc<FMT, NW, 2>(p, wc_force ? wc_force : g_wc[1], sms, stream);
+  return launch_wc<FMT, NW, 4>(p, wc_force ? wc_force : g_wc[2], sms, stream);
 }
 
 }  // namespace
@@ -547,33 +547,42 @@ int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages) {
   return BT_OK;
 }
 
-int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2, uint64_t add,
-                float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base, uint64_t work,
-                size_t work_bytes, uint64_t stream) {
-  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_gemv_bfp: weights must be bfp8 (8) or bfp4 (4), not %d", fmt);
-  BT_REQUIRE(epilogue >= BT_EPI_NONE && epilogue <= BT_EPI_ARGMAX, "bt_gemv_bfp: unknown epilogue %d", epilogue);
-  BT_REQUIRE(M >= 1 && M <= 32, "bt_gemv_bfp: takes 1 to 32 rows of x, not %d", M);
-  BT_REQUIRE(K > 0 && N > 0 && K % 32 == 0 && N % 32 == 0, "bt_gemv_bfp: K and N must be positive multiples of 32: %d x %d", K, N);
-  BT_REQUIRE(x && w && x % 16 == 0 && w % 16 == 0, "bt_gemv_bfp: x and w must be 16-byte aligned device addresses");
-  BT_REQUIRE((epilogue == BT_EPI_GLU) == (w2 != 0) && w2 % 16 == 0, "bt_gemv_bfp: w2 goes with the GLU epilogue, and only with it");
-  BT_REQUIRE(add % 4 == 0, "bt_gemv_bfp: the addend must be 4-byte aligned");
-  if (epilogue == BT_EPI_ARGMAX) BT_REQUIRE(arg_val && arg_idx, "bt_gemv_bfp: the argmax epilogue needs arg_val and arg_idx");
-  else BT_REQUIRE(out && out % 8 == 0 && (out_dtype == BT_BF16 || out_dtype == BT_FP32), "bt_gemv_bfp: needs an 8-byte aligned bf16 or fp32 result");
-  BT_REQUIRE(work && work % 16 == 0 && work_bytes >= kWsBytes, "bt_gemv_bfp: needs %zu bytes of 16-byte aligned scratch, got %zu", kWsBytes, work_bytes);
-  BT_REQUIRE((N / 32 + 3) / 4 <= kMaxSubPanels, "bt_gemv_bfp: N = %d is past the %d columns one launch handles", N, kMaxSubPanels * 128);
+// Argument checks and the launch shared by the entry points. `scratch` carries the scratch pointers; wc_force, when
+// nonzero, fixes the sub-panel width.
+static int gemv_common(const char *who, int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
+                       uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base,
+                       const GemvParams &scratch, int wc_force, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "%s: weights must be bfp8 (8) or bfp4 (4), not %d", who, fmt);
+  BT_REQUIRE(epilogue >= BT_EPI_NONE && epilogue <= BT_EPI_ARGMAX, "%s: unknown epilogue %d", who, epilogue);
+  BT_REQUIRE(M >= 1 && M <= 32, "%s: takes 1 to 32 rows of x, not %d", who, M);
+  BT_REQUIRE(K > 0 && N > 0 && K % 32 == 0 && N % 32 == 0, "%s: K and N must be positive multiples of 32: %d x %d", who, K, N);
+  BT_REQUIRE(x && w && x % 16 == 0 && w % 16 == 0, "%s: x and w must be 16-byte aligned device addresses", who);
+  BT_REQUIRE((epilogue == BT_EPI_GLU) == (w2 != 0) && w2 % 16 == 0, "%s: w2 goes with the GLU epilogue, and only with it", who);
+  BT_REQUIRE(add % 4 == 0, "%s: the addend must be 4-byte aligned", who);
+  if (epilogue == BT_EPI_ARGMAX) BT_REQUIRE(arg_val && arg_idx, "%s: the argmax epilogue needs arg_val and arg_idx", who);
+  else BT_REQUIRE(out && out % 8 == 0 && (out_dtype == BT_BF16 || out_dtype == BT_FP32), "%s: needs an 8-byte aligned bf16 or fp32 result", who);
   if (int s = use_device(device)) return s;
   int sms = 0;
   BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  GemvParams p{};
+  GemvParams p = scratch;
   p.x = as_ptr<uint8_t>(x), p.w[0] = as_ptr<uint8_t>(w), p.w[1] = as_ptr<uint8_t>(w2), p.add = as_ptr<uint16_t>(add);
   p.out = as_ptr<void>(out), p.arg_val = as_ptr<float>(arg_val), p.arg_idx = as_ptr<int>(arg_idx);
-  p.error = as_ptr<int>(work + kWsError), p.panels_done = as_ptr<int>(work + kWsPanelsDone), p.counters = as_ptr<int>(work + kWsCounters);
-  p.part_val = as_ptr<float>(work + kWsArgVal), p.part_idx = as_ptr<int>(work + kWsArgIdx), p.partials = as_ptr<float>(work + kWsPartials);
   p.trace = g_trace;
   p.alpha = alpha, p.arg_base = arg_base, p.M = M, p.KT = K / 32, p.TC = N / 32, p.epi = epilogue, p.out_fp32 = out_dtype == BT_FP32;
   cudaStream_t st = as_stream(stream);
-  if (fmt == BT_BFP8) return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP8, 2>(p, sms, st) : launch_tg<BT_BFP8, 1>(p, sms, st);
-  return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP4, 2>(p, sms, st) : launch_tg<BT_BFP4, 1>(p, sms, st);
+  if (fmt == BT_BFP8) return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP8, 2>(p, wc_force, sms, st) : launch_tg<BT_BFP8, 1>(p, wc_force, sms, st);
+  return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP4, 2>(p, wc_force, sms, st) : launch_tg<BT_BFP4, 1>(p, wc_force, sms, st);
+}
+
+int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2, uint64_t add,
+                float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base, uint64_t work,
+                size_t work_bytes, uint64_t stream) {
+  BT_REQUIRE(work && work % 16 == 0 && work_bytes >= kWsBytes, "bt_gemv_bfp: needs %zu bytes of 16-byte aligned scratch, got %zu", kWsBytes, work_bytes);
+  BT_REQUIRE(N <= 0 || (N / 32 + 3) / 4 <= kMaxSubPanels, "bt_gemv_bfp: N = %d is past the %d columns one launch handles", N, kMaxSubPanels * 128);
+  GemvParams scratch{};
+  scratch.error = as_ptr<int>(work + kWsError), scratch.panels_done = as_ptr<int>(work + kWsPanelsDone), scratch.counters = as_ptr<int>(work + kWsCounters);
+  scratch.part_val = as_ptr<float>(work + kWsArgVal), scratch.part_idx = as_ptr<int>(work + kWsArgIdx), scratch.partials = as_ptr<float>(work + kWsPartials);
+  return gemv_common("bt_gemv_bfp", device, fmt, epilogue, M, K, N, x, w, w2, add, alpha, out, out_dtype, arg_val, arg_idx, arg_base, scratch, 0, stream);
 }
 
 // Debugging aid: when `buffer` is nonzero, every later launch writes 8 nanosecond timestamps per CTA into it (kernel
