@@ -294,7 +294,7 @@ def _streamed(w):
   return w._stream
 
 
-def _launch_matmul(rt, e, epilogue, out, rows, arg=(0, 0)):
+def _launch_matmul(rt, e, epilogue, out, rows, arg=(0, 0), arg_base=0):
   x, w = e["x"].realize(), _streamed(e["w"])
   w2 = _streamed(e["w2"]) if e.get("w2") is not None else None
   add = e["add"].realize() if e["add"] is not None else None
@@ -307,5 +307,5 @@ def _launch_matmul(rt, e, epilogue, out, rows, arg=(0, 0)):
     m, tr = min(32, rows - i), i // 32
     rt.launch("bt_gemv_bfp", (fmt, EPILOGUE[epilogue], m, K, N, x.addr + tr * x.tc * 2048, w.addr, w2.addr if w2 else 0,
                               (add.addr + (tr * add.tc * 2048 if add.rows > 1 else 0)) if add else 0, ctypes.c_float(e["alpha"]),
-                              (out.addr + tr * out.tc * osize) if out is not None else 0, out_dtype, arg[0], arg[1], 0,
+                              (out.addr + tr * out.tc * osize) if out is not None else 0, out_dtype, arg[0], arg[1], arg_base,
                               rt.work, rt.work_bytes), name=name)
