@@ -525,6 +525,23 @@ int launch_tg(const GemvParams &p, int wc_force, int sms, cudaStream_t stream) {
 
 }  // namespace
 
+// ---- the entry point that allocates nothing -------------------------------------------------------------------
+// Scratch for bt_gemv_bfp_static lives in this array, inside the library's device image, so a caller that may
+// not allocate device memory still has somewhere for the kernel's counters and partial sums. Every device that
+// loads the library holds these bytes until the process exits. The layout mirrors the caller-provided workspace
+// at reduced limits: up to 8 rows of x, up to kStaticSubPanels sub-panels of 4 tile columns.
+namespace {
+constexpr int kStaticSubPanels = 4096;                                  // N <= 4096 * 4 * 32 = 524288 columns
+constexpr size_t kStaticSlotFloats = 4 * 16 * 32;                       // WC = 4, up to 16 accumulators per lane
+constexpr size_t kStCounters = 256;
+constexpr size_t kStControlBytes = kStCounters + 4 * (size_t)kStaticSubPanels;   // what must be zero when a call starts
+constexpr size_t kStArgVal = kStControlBytes;
+constexpr size_t kStArgIdx = kStArgVal + 4 * 32 * (size_t)kStaticSubPanels;
+constexpr size_t kStPartials = kStArgIdx + 4 * 32 * (size_t)kStaticSubPanels;
+constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 3.1 MB
+}  // namespace
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
 extern "C" {
 
 int bt_gemv_workspace_bytes(int device, size_t *bytes) {
@@ -583,6 +600,42 @@ int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
   scratch.error = as_ptr<int>(work + kWsError), scratch.panels_done = as_ptr<int>(work + kWsPanelsDone), scratch.counters = as_ptr<int>(work + kWsCounters);
   scratch.part_val = as_ptr<float>(work + kWsArgVal), scratch.part_idx = as_ptr<int>(work + kWsArgIdx), scratch.partials = as_ptr<float>(work + kWsPartials);
   return gemv_common("bt_gemv_bfp", device, fmt, epilogue, M, K, N, x, w, w2, add, alpha, out, out_dtype, arg_val, arg_idx, arg_base, scratch, 0, stream);
+}
+
+// The device address of g_static_scratch on `device`, looked up once per device. In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address comes from
+// cudaGetSymbolAddress, asked with that device current.
+static int static_scratch(int device, unsigned char **base) {
+  static unsigned char *bases[64] = {};
+  BT_REQUIRE(device >= 0 && device < 64, "bt_gemv_bfp_static: device %d is out of range", device);
+  if (!bases[device]) {
+    if (int s = use_device(device)) return s;
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr) return fail(BT_DEVICE, "bt_gemv_bfp_static: no address for the built-in scratch on device %d: %s", device, cudaGetErrorString(e));
+    bases[device] = static_cast<unsigned char *>(ptr);
+  }
+  *base = bases[device];
+  return BT_OK;
+}
+
+int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2, uint64_t add,
+                       float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base, uint64_t stream) {
+  BT_REQUIRE(M <= 8, "bt_gemv_bfp_static: the built-in scratch holds up to 8 rows of x, not %d; use bt_gemv_bfp with your own scratch", M);
+  BT_REQUIRE(N <= kStaticSubPanels * 128, "bt_gemv_bfp_static: the built-in scratch holds up to %d columns, not %d; use bt_gemv_bfp with your own scratch",
+             kStaticSubPanels * 128, N);
+  unsigned char *base = nullptr;
+  if (int s = static_scratch(device, &base)) return s;
+  if (int s = use_device(device)) return s;
+  // the array keeps whatever the last call left: flags and arrival counters must start at zero
+  BT_CUDA(cudaMemsetAsync(base, 0, kStControlBytes, as_stream(stream)));
+  GemvParams scratch{};
+  scratch.error = reinterpret_cast<int *>(base), scratch.panels_done = reinterpret_cast<int *>(base + 4);
+  scratch.counters = reinterpret_cast<int *>(base + kStCounters);
+  scratch.part_val = reinterpret_cast<float *>(base + kStArgVal), scratch.part_idx = reinterpret_cast<int *>(base + kStArgIdx);
+  scratch.partials = reinterpret_cast<float *>(base + kStPartials);
+  return gemv_common("bt_gemv_bfp_static", device, fmt, epilogue, M, K, N, x, w, w2, add, alpha, out, out_dtype, arg_val, arg_idx, arg_base, scratch,
+                     4, stream);
 }
 
 // Debugging aid: when `buffer` is nonzero, every later launch writes 8 nanosecond timestamps per CTA into it (kernel

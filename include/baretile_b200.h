@@ -113,6 +113,20 @@ int bt_gemv_workspace_bytes(int device, size_t *bytes);
 int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
                 uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx,
                 int arg_base, uint64_t work, size_t work_bytes, uint64_t stream);
+/* The same matmul for callers that cannot allocate device memory: it has no counterpart in the reference.
+ * Some embedders of this library run where cudaMalloc is off limits -- inside another framework's capture or
+ * allocator-owned region, in a process whose memory budget was handed out in full at start-up, or in a plug-in
+ * that is only ever given its input and output buffers. For them the scratch that bt_gemv_bfp takes from the
+ * caller sits in a fixed array inside the library's device image (about 3.1 MB on every GPU that loads the
+ * library, held until the process exits). The call allocates and frees nothing, on the host side either.
+ * Limits, rejected with BT_BAD_ARGUMENT: M <= 8 rows of x, N <= 524288 columns. Inputs and outputs are the
+ * caller's, exactly as for bt_gemv_bfp. The first call on a device looks the array's address up (one runtime
+ * query); make that first call outside any stream capture. All calls on a device share the one array and each
+ * call first clears the flags and counters it keeps there, so two calls whose kernels overlap on the GPU (different
+ * streams) race: keep them on one stream or serialise them. */
+int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
+                       uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx,
+                       int arg_base, uint64_t stream);
 /* Nonzero in *error once a bounded wait inside a launch that used this scratch gave up (its results are then
  * unreliable): the counterpart of Runtime.wait's timeout report (baretile/runtime.py:866-876). Synchronises the
  * stream, and clears the flag. */
