@@ -1,0 +1,281 @@
+// Prefill matmul for many token rows: out = epilogue(alpha * x @ W), W block-float in streaming layout.
+//
+// With hundreds of rows the contraction is dense and belongs on the 5th-generation tensor cores. One CTA computes a
+// 256 x 256 block of x @ W (two 128-row halves, each an fp32 accumulator of 256 columns in tensor memory, 512 columns
+// in all). For a gate/up pair the 256 MMA columns are 128 columns of Wg next to the same 128 columns of Wu, and the
+// epilogue writes silu(gate) * up for 128 output columns.
+//
+// Per 64-deep K block:
+//   warp 0   (producer)  TMA-loads the two 128 x 64 tiles of x (row-major bf16, 128-byte swizzle) and bulk-copies the
+//                        block's 16 packed weight tiles (two runs of the streaming layout) into a ring.
+//   warps 2-9 (dequant)  each takes one tile column: reads its two packed tiles, expands them to exact bf16 in
+//                        registers the way the decode kernel does (byte permutes, then a packed multiply by the face
+//                        row's power of two), and stores them into the B tile in the K-major 128-byte-swizzled layout
+//                        the MMA reads. The weights carry a factor 2^-64, undone in the epilogue.
+//   warp 1   (MMA)       one lane issues 2 x 4 tcgen05.mma (128 x 256 x 16 each) and commits; the commit frees the
+//                        stage for the producer and the dequant warps.
+// After the last K block the dequant warps become the epilogue: tcgen05.ld brings 32 rows x 32 columns per warp into
+// registers, the activation is applied, and bf16 (rounded half up) or fp32 goes out in tile layout.
+// Every wait is bounded and reports through the error word instead of hanging.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "stream_layout.cuh"
+#include "tmap.cuh"
+#include <cstring>
+
+using namespace bt;
+
+namespace {
+
+constexpr int kBM = 256, kBN = 256, kBK = 64;            // CTA tile; BN counts MMA columns
+constexpr int kStagesAB = 2, kStagesP = 4;
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (2 + kDequantWarps) * 32;
+constexpr uint32_t kWaitLimit = 1u << 14;                // attempts of up to 100 us each
+
+constexpr int kABytes = 128 * 128;                       // one 128-row half of x for a K block: 128 rows x 128 bytes
+constexpr int kBBytes = kBN * 128;                       // the expanded weights for a K block
+constexpr int kStageAB = 2 * kABytes + kBBytes;          // 64 KiB
+
+struct GemmParams {
+  const uint8_t *w[2];       // packed weights by columns; w[1] only for the gate/up pair
+  const uint16_t *add;       // unused for now
+  void *out;
+  int *error;
+  float alpha;
+  int M, KT, TC, epi, out_fp32, pair;
+};
+
+template <int FMT>
+struct Layout {
+  static constexpr int TB = tile_bytes(FMT);
+  static constexpr int P_STAGE = 16 * TB;                 // packed tiles of one K block: 2 tile rows x 8 tile columns
+  static constexpr int AB0 = 1024;                        // barriers and the tensor-memory address live below
+  static constexpr int P0 = AB0 + kStagesAB * kStageAB;
+  static constexpr int BYTES = P0 + kStagesP * P_STAGE;
+};
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+template <int HI>
+__device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
+  return prmt(ew, 0u, HI ? 0x4342u : 0x4140u) * 128u + 0x1F801F80u;   // bf16 lanes 2^(e - 64)
+}
+__device__ __forceinline__ float silu(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+__device__ __forceinline__ uint32_t bf16_half_up(float v) { return (__float_as_uint(v) + 0x8000u) >> 16; }
+
+// Expand one packed tile (streaming layout, shared address `tile`) to bf16 and store it as rows [32 c, 32 c + 32) and
+// K columns [32 j, 32 j + 32) of the B tile at shared address `b` (K-major, 128-byte rows, 128-byte swizzle: the
+// 16-byte chunk index of a row is XORed with the row's index modulo 8).
+template <int FMT>
+__device__ __forceinline__ void expand_tile(uint32_t tile, uint32_t b, int c, int j, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint4 ev = lds128(tile + t * 16);
+  const uint32_t ee[4] = {ev.x, ev.y, ev.z, ev.w};
+  uint4 wv[2];
+  if (FMT == BT_BFP8) wv[0] = lds128(tile + 64 + lane * 16), wv[1] = lds128(tile + 64 + 512 + lane * 16);
+  else wv[0] = lds128(tile + 64 + lane * 16), wv[1] = wv[0];
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+#pragma unroll
+    for (int fs = 0; fs < 2; fs++) {
+      const uint32_t ew = ee[2 * h + fs];
+      const uint32_t s01 = scale_pair<0>(ew), s23 = scale_pair<1>(ew);
+      uint32_t m0, s0, m1, s1;   // magnitude and sign bytes of channels 2g and 2g + 1, four consecutive k each
+      if (FMT == BT_BFP8) {
+        const uint32_t w0 = fs ? wv[h].z : wv[h].x, w1 = fs ? wv[h].w : wv[h].y;
+        m0 = w0 & 0x7F7F7F7Fu, s0 = w0 & 0x80808080u, m1 = w1 & 0x7F7F7F7Fu, s1 = w1 & 0x80808080u;
+      } else {
+        const uint32_t wb = h ? (fs ? wv[0].w : wv[0].z) : (fs ? wv[0].y : wv[0].x), wl = wb << 4;
+        m0 = wl & 0x70707070u, s0 = wl & 0x80808080u, m1 = wb & 0x70707070u, s1 = wb & 0x80808080u;
+      }
+      const uint32_t a0 = mul_bf16x2(prmt(m0, s0, 0x5140u), s01), a1 = mul_bf16x2(prmt(m1, s1, 0x5140u), s01);
+      const uint32_t a2 = mul_bf16x2(prmt(m0, s0, 0x7362u), s23), a3 = mul_bf16x2(prmt(m1, s1, 0x7362u), s23);
+      const int n0 = 32 * c + 16 * fs + 2 * g;                       // even, so n0 and n0 + 1 share an 8-row group
+      const int chunk = 4 * j + 2 * h + (t >> 1);                    // 16-byte chunk of k = 32 j + 16 h + 4 t
+      const uint32_t group = b + (n0 >> 3) * 1024 + (t & 1) * 8;
+      sts64(group + (n0 & 7) * 128 + ((chunk ^ (n0 & 7)) << 4), a0, a2);
+      sts64(group + ((n0 + 1) & 7) * 128 + ((chunk ^ ((n0 + 1) & 7)) << 4), a1, a3);
+    }
+  }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap) {
+  using L = Layout<FMT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);   // swizzled tiles want 1024-byte alignment
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t full0 = sb, empty0 = sb + 16, pfull0 = sb + 32, pempty0 = sb + 64, acc_full = sb + 96, tmem_slot = sb + 112;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = p.KT / 2;                                          // K blocks of 64
+  const int m0 = blockIdx.x * kBM;                                  // first row of this CTA's block
+  const int bc = blockIdx.y;                                        // block column: 128 output columns (pair) or 256
+  auto a_tile = [&](int s, int mh) { return sb + L::AB0 + s * kStageAB + mh * kABytes; };
+  auto b_tile = [&](int s) { return sb + L::AB0 + s * kStageAB + 2 * kABytes; };
+  auto p_stage = [&](int ps) { return sb + L::P0 + ps * L::P_STAGE; };
+  auto wait = [&](uint32_t bar, uint32_t parity, int code) {
+    if (!mbar_wait(bar, parity, kWaitLimit)) atomicExch(p.error, code);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesAB; s++) mbar_init(full0 + 8 * s, 1 + kDequantWarps), mbar_init(empty0 + 8 * s, 1);
+    for (int s = 0; s < kStagesP; s++) mbar_init(pfull0 + 8 * s, 1), mbar_init(pempty0 + 8 * s, kDequantWarps);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(smem + 112);
+
+  if (warp == 0) {
+    // ---- producer ----
+    if (lane == 0) {
+      auto packed = [&](int kb) {           // the K block's 16 packed tiles: two runs of 2 tile rows x 4 tiles
+        const int ps = kb % kStagesP;
+        if (kb >= kStagesP) wait(pempty0 + 8 * ps, (kb / kStagesP - 1) & 1, 11);
+        mbar_expect_tx(pfull0 + 8 * ps, L::P_STAGE);
+        for (int i = 0; i < 2; i++) {
+          const uint8_t *w = p.pair ? p.w[i] : p.w[0];
+          const int run = p.pair ? bc : 2 * bc + i;
+          bulk_g2s(p_stage(ps) + i * 8 * L::TB, w + ((size_t)run * kPanel * p.KT + (size_t)(2 * kb) * kPanel) * L::TB, 8 * L::TB, pfull0 + 8 * ps);
+        }
+      };
+      for (int kb = 0; kb < min(KB, kStagesP - 1); kb++) packed(kb);
+      for (int kb = 0; kb < KB; kb++) {
+        if (kb + kStagesP - 1 < KB) packed(kb + kStagesP - 1);
+        const int s = kb % kStagesAB;
+        if (kb >= kStagesAB) wait(empty0 + 8 * s, (kb / kStagesAB - 1) & 1, 12);
+        mbar_expect_tx(full0 + 8 * s, 2 * kABytes);
+        tma_load_2d(a_tile(s, 0), &amap, kb * kBK, m0, full0 + 8 * s);          // rows past M read as zeros
+        tma_load_2d(a_tile(s, 1), &amap, kb * kBK, m0 + 128, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      for (int kb = 0; kb < KB; kb++) {
+        const int s = kb % kStagesAB;
+        wait(full0 + 8 * s, (kb / kStagesAB) & 1, 13);
+        tc_fence_after();
+#pragma unroll
+        for (int mh = 0; mh < 2; mh++) {
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++)
+            umma_bf16(tmem + mh * kBN, smem_desc(a_tile(s, mh) + kk * 32), smem_desc(b_tile(s) + kk * 32), kIdesc, (kb | kk) != 0);
+        }
+        umma_commit(empty0 + 8 * s);
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    // ---- dequant warps, then the epilogue ----
+    const int d = warp - 2;
+    for (int kb = 0; kb < KB; kb++) {
+      const int ps = kb % kStagesP, s = kb % kStagesAB;
+      wait(pfull0 + 8 * ps, (kb / kStagesP) & 1, 14);
+      if (kb >= kStagesAB) wait(empty0 + 8 * s, (kb / kStagesAB - 1) & 1, 15);
+      tc_fence_after();
+#pragma unroll
+      for (int j = 0; j < 2; j++) expand_tile<FMT>(p_stage(ps) + ((d >> 2) * 8 + j * 4 + (d & 3)) * L::TB, b_tile(s), d, j, lane);
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full0 + 8 * s), mbar_arrive(pempty0 + 8 * ps);
+    }
+    wait(acc_full, 0, 16);
+    tc_fence_after();
+    const int q = warp & 3, ch = d >> 2;                            // tensor-memory lane quarter; column half
+    const float unscale = 18446744073709551616.f * p.alpha;         // 2^64: the weights were expanded times 2^-64
+    const int out_cols = p.pair ? 128 : 256, chunks = out_cols / 64;  // 32-column chunks for this warp
+    const int tc_out = p.TC, tile_rows = (p.M + 31) / 32;
+#pragma unroll 1
+    for (int mh = 0; mh < 2; mh++) {
+      const int row = m0 + 128 * mh + 32 * q + lane, tr = row >> 5;
+      if (m0 + 128 * mh + 32 * q >= tile_rows * 32) continue;       // the whole warp is past the tensor's tile rows
+#pragma unroll 1
+      for (int cc = 0; cc < chunks; cc++) {
+        const int col = ch * (out_cols / 2) + 32 * cc;              // first output column of the chunk, within the block
+        uint32_t v[32], u[32];
+        tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + mh * kBN + col, v);
+        if (p.pair) tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + mh * kBN + 128 + col, u);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          float x = __uint_as_float(v[i]) * unscale;
+          if (p.pair) x = silu(x) * (__uint_as_float(u[i]) * unscale);
+          else if (p.epi == BT_EPI_RELU) x = fmaxf(x, 0.f);
+          else if (p.epi == BT_EPI_SILU) x = silu(x);
+          f[i] = row < p.M ? x : 0.f;
+        }
+        const size_t tile = (size_t)tr * tc_out + (size_t)bc * (out_cols / 32) + (col >> 5);
+        const int in_tile = ((row >> 4) & 1) * 512 + (row & 15) * 16;    // datum index of (row, 0) in the tile
+        if (p.out_fp32) {
+          float *o = static_cast<float *>(p.out) + tile * 1024 + in_tile;
+#pragma unroll
+          for (int fcol = 0; fcol < 2; fcol++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+              reinterpret_cast<float4 *>(o + fcol * 256)[i] = make_float4(f[16 * fcol + 4 * i], f[16 * fcol + 4 * i + 1], f[16 * fcol + 4 * i + 2], f[16 * fcol + 4 * i + 3]);
+        } else {
+          uint16_t *o = static_cast<uint16_t *>(p.out) + tile * 1024 + in_tile;
+#pragma unroll
+          for (int fcol = 0; fcol < 2; fcol++)
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+              uint32_t w[4];
+#pragma unroll
+              for (int k = 0; k < 4; k++) w[k] = bf16_half_up(f[16 * fcol + 8 * i + 2 * k]) | bf16_half_up(f[16 * fcol + 8 * i + 2 * k + 1]) << 16;
+              reinterpret_cast<uint4 *>(o + fcol * 256)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+extern "C" {
+
+int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t a, uint64_t w, uint64_t w2, float alpha, uint64_t out,
+                int out_dtype, uint64_t work, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_gemm_bfp: weights must be bfp8 (8) or bfp4 (4), not %d", fmt);
+  BT_REQUIRE(epilogue >= BT_EPI_NONE && epilogue <= BT_EPI_GLU, "bt_gemm_bfp: the epilogue is none, relu, silu or glu, not %d", epilogue);
+  const bool pair = epilogue == BT_EPI_GLU;
+  BT_REQUIRE(M >= 1 && K > 0 && N > 0 && K % 64 == 0, "bt_gemm_bfp: needs M >= 1 and K a positive multiple of 64: %d x %d", M, K);
+  BT_REQUIRE(N % (pair ? 128 : 256) == 0, "bt_gemm_bfp: N must be a multiple of %d, not %d", pair ? 128 : 256, N);
+  BT_REQUIRE(a && w && out && work && a % 16 == 0 && w % 16 == 0 && out % 16 == 0, "bt_gemm_bfp: needs 16-byte aligned device addresses");
+  BT_REQUIRE(pair == (w2 != 0) && w2 % 16 == 0, "bt_gemm_bfp: w2 goes with the GLU epilogue, and only with it");
+  BT_REQUIRE(out_dtype == BT_BF16 || out_dtype == BT_FP32, "bt_gemm_bfp: results are bf16 or fp32");
+  if (int s = use_device(device)) return s;
+  alignas(64) CUtensorMap amap;
+  const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M}, strides[1] = {(uint64_t)K * 2};
+  const uint32_t box[2] = {kBK, 128};
+  if (int s = make_tmap(&amap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, as_ptr<void>(a), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return s;
+  GemmParams p{};
+  p.w[0] = as_ptr<uint8_t>(w), p.w[1] = as_ptr<uint8_t>(w2), p.out = as_ptr<void>(out), p.error = as_ptr<int>(work);
+  p.alpha = alpha, p.M = M, p.KT = K / 32, p.TC = N / 32, p.epi = epilogue, p.out_fp32 = out_dtype == BT_FP32, p.pair = pair;
+  const dim3 grid((M + kBM - 1) / kBM, N / (pair ? 128 : 256));
+  static bool configured[64] = {};
+  if (!configured[device & 63]) {
+    BT_CUDA(cudaFuncSetAttribute(gemm_kernel<BT_BFP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<BT_BFP8>::BYTES + 1024));
+    BT_CUDA(cudaFuncSetAttribute(gemm_kernel<BT_BFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<BT_BFP4>::BYTES + 1024));
+    configured[device & 63] = true;
+  }
+  if (fmt == BT_BFP8) gemm_kernel<BT_BFP8><<<grid, kThreads, Layout<BT_BFP8>::BYTES + 1024, as_stream(stream)>>>(p, amap);
+  else gemm_kernel<BT_BFP4><<<grid, kThreads, Layout<BT_BFP4>::BYTES + 1024, as_stream(stream)>>>(p, amap);
+  return launched("gemm_kernel");
+}
+
+}  // extern "C"

@@ -303,6 +303,15 @@ def _launch_matmul(rt, e, epilogue, out, rows, arg=(0, 0), arg_base=0):
   osize = tile_bytes(out.dtype) if out is not None else 0
   name = f"matmul {w.dtype} {epilogue}"
   if epilogue == "argmax" and rows > 32: raise ValueError("the fused pick takes up to 32 rows")
+  if rows > 32 and add is None and epilogue != "argmax" and K % 64 == 0 and N % (128 if w2 else 256) == 0:
+    # many rows: the tensor-core kernel, which reads x row-major
+    flat = rt.dram_alloc(2 * rows * K)
+    try:
+      rt.launch("bt_untilize", (2, x.addr, flat, 1, rows, K), name="rows")
+      rt.launch("bt_gemm_bfp", (fmt, EPILOGUE[epilogue], rows, K, N, flat, w.addr, w2.addr if w2 else 0, ctypes.c_float(e["alpha"]),
+                                out.addr, out_dtype, rt.work), name=f"prefill {w.dtype} {epilogue}")
+    finally: rt.dram_free(flat)
+    return
   for i in range(0, rows, 32):   # one launch per tile row of x; each streams W once
     m, tr = min(32, rows - i), i // 32
     rt.launch("bt_gemv_bfp", (fmt, EPILOGUE[epilogue], m, K, N, x.addr + tr * x.tc * 2048, w.addr, w2.addr if w2 else 0,

@@ -113,6 +113,17 @@ int bt_gemv_workspace_bytes(int device, size_t *bytes);
 int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
                 uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx,
                 int arg_base, uint64_t work, size_t work_bytes, uint64_t stream);
+/* ---- the matmul: fused_kernel's prefill grid (baretile/kernels.py:205-215, :470-506, grid_parts :18-39) ----
+ * out[M, N] = epilogue(alpha * (a[M, K] @ W[K, N])) for many rows, on the tcgen05 tensor cores with fp32
+ * accumulators in tensor memory. The weights are expanded from block float to exact bf16 inside the kernel.
+ *   a      bf16, ROW-MAJOR [M, K] (bt_untilize of the tile-layout tensor); K a multiple of 64.
+ *   w, w2  block-float weights in streaming layout; w2 only for BT_EPI_GLU (out = silu(a @ w) * (a @ w2)).
+ *          N a multiple of 256, or of 128 for the pair.
+ *   out    bf16 or fp32 tiles, rows past M zero.
+ *   work   the matmul scratch (bt_gemv_workspace_bytes): only its error word is used. */
+int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t a, uint64_t w, uint64_t w2, float alpha,
+                uint64_t out, int out_dtype, uint64_t work, uint64_t stream);
+
 /* The same matmul for callers that cannot allocate device memory: it has no counterpart in the reference.
  * Some embedders of this library run where cudaMalloc is off limits -- inside another framework's capture or
  * allocator-owned region, in a process whose memory budget was handed out in full at start-up, or in a plug-in
