@@ -274,6 +274,39 @@ def main():
                "frac_of_sustained_peak": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"], 3),
                "includes": "the row-major copy of x and of h that feeds the TMA loads (2 small launches per step)"}
 
+  # ---- the sharded configurations (configs[3], configs[4]): layers split over the ranks, with their exchanges ----
+  sharded = None
+  if dist is not None:
+    from baretile_b200 import dist as bd
+    def tiled(rows, cols, seed):      # bf16 bits of a rows x cols matrix, a 1024 x 1024 N(0, 0.02) block repeated
+      block = rounded(np.random.default_rng(seed), (1024, 1024), 0.02, True)
+      return np.tile(block, (-(-rows // 1024), -(-cols // 1024)))[:rows, :cols]
+    def shard(rows, cols, seed, fmt): return Tensor.frombytes(rt, rows, cols, np.ascontiguousarray(tiled(rows, cols, seed)).tobytes()).cast(fmt).columns()
+    K3, N3, V4 = 8192, 28672, 128256
+    a, b = bd.split_tiles(N3, world, rank)
+    mlp = bd.ShardedMLP(rt, shard(K3, b - a, 1, "bfp4"), shard(K3, b - a, 2, "bfp4"), shard(b - a, K3, 3, "bfp4"))
+    va, vb = bd.split_tiles(V4, world, rank)
+    head = bd.ShardedHead(rt, shard(K3, vb - va, 4, "bfp8"), va)
+    sharded = {"mlp": [], "head": []}
+    for m in (1, 4, 16):
+      xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
+      for gather in (True, False):
+        fn = lambda: mlp.forward(xs, gather=gather)
+        for _ in range(3): fn()
+        ms_ = timed(fn, 10) / 10
+        total = 3 * (K3 // 32) * (N3 // 32) * TILE["bfp4"]
+        sharded["mlp"].append({"M": m, "all_gather": gather, "us": round(ms_ * 1e3, 1), "GBps_all_ranks": round(total / (ms_ * 1e-3) / 1e9, 1)})
+    for m in (1, 4, 8):
+      xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
+      fn = lambda: head.pick(xs)
+      for _ in range(3): fn()
+      ms_ = timed(fn, 10) / 10
+      total = (K3 // 32) * (V4 // 32) * TILE["bfp8"]
+      sharded["head"].append({"M": m, "us": round(ms_ * 1e3, 1), "GBps_all_ranks": round(total / (ms_ * 1e-3) / 1e9, 1)})
+    sharded["note"] = ("configs[3]: gate/up [8192,28672] bfp4 split over N, down [28672,8192] split over K, all-reduce of fp32 partials, with or "
+                       "without the all-gather between them; configs[4]: LM head [8192,128256] bfp8 split over the vocabulary, fused argmax, "
+                       "pairs gathered over NCCL; times are the max over ranks, bytes are the packed weights of all ranks")
+
   if dist is not None: dist.barrier()
   if rank == 0:
     line = {"metric": "decode GEMV achieved HBM GB/s (bfp8/bfp4, Llama-3-8B shapes)", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
@@ -290,7 +323,7 @@ def main():
                          "of": peak_kind, "kernel": "gemv_kernel: bytes per launch / average launch duration over the event-timed region (24 launches per replayed step)",
                          "per_launch_events_GBps": round(per_launch_sum, 1),
                          "frac_of_spec_8TBps": round(achieved / 8000, 3)},
-            "prefill": prefill, "cases": table}
+            "prefill": prefill, "sharded": sharded, "cases": table}
     if not args.no_cpu:
       v, dt, sample = cpu_sample()
       line["cpu_baseline"] = {"value": round(v, 3), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample}
