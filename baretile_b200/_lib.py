@@ -4,9 +4,9 @@ The reference binds its device library the same way: ctypes.CDLL with explicit a
 (baretile/pci.py:52-63). Status codes become the exceptions the reference raises for the same conditions
 (docs/api.md:51-62): bad argument -> ValueError, device or state -> RuntimeError, timeout -> TimeoutError,
 out of memory -> MemoryError."""
-import ctypes, pathlib
+import ctypes, os, pathlib
 
-PATH = pathlib.Path(__file__).resolve().parent / "libbaretile_b200.so"
+PATH = pathlib.Path(os.environ.get("BARETILE_B200_LIB") or pathlib.Path(__file__).resolve().parent / "libbaretile_b200.so")
 u64, i32, f32, size_t, vp = ctypes.c_uint64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_void_p
 
 

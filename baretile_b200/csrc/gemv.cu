@@ -69,7 +69,7 @@ struct Config {
   static constexpr int CW = WC == 12 ? 12 : 16;
   static constexpr int THREADS = (CW + 1) * 32;
   static constexpr int KS = CW / WC;                             // k-slices: warps sharing a column
-  static constexpr int T = NW == 2 ? 1 : 2;                      // tile rows a warp takes per stage
+  static constexpr int T = NW == 2 ? 1 : (FMT == BT_BFP4 && TG == 1 ? 4 : 2);   // tile rows a warp takes per stage
   static constexpr int UPS = KS * T;                             // units (tile rows) per stage
   static constexpr int TB = tile_bytes(FMT);
   static constexpr int XB = TG == 1 ? 512 : TG == 2 ? 1024 : 2048;  // bytes of an x tile staged: rows 0-7, 0-15 or all 32
@@ -335,14 +335,28 @@ __global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_ke
       const int col = sp * WC + cc;
       if (col < p.TC) {
         const int width = min(kPanel, p.TC - (sp * RPS + cc / kPanel) * kPanel);   // tiles of a tile row in this run
-        const uint32_t so = s * C::STAGE + ck * width * C::TB, xo = s * C::STAGE + ck * C::XB;
+        if (n == C::UPS && width == kPanel) {
+          // a full stage of a full run: every offset is a compile-time constant
+          const uint32_t so = s * C::STAGE + ck * (kPanel * C::TB), xo = s * C::STAGE + ck * C::XB;
 #pragma unroll
-        for (int j = 0; j < C::T; j++) {                        // this warp's tile rows of the stage: ck, ck + KS, ...
-          if (ck + j * C::KS < n) {
+          for (int j = 0; j < C::T; j++) {
 #pragma unroll
             for (int m = 0; m < NW; m++) {
-              const uint32_t o = so + (m * RPS * C::UPS * kPanel + j * C::KS * width) * C::TB;
-              tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + xo + j * C::KS * C::XB, acc[m]);
+              constexpr int kMatrix = RPS * C::UPS * kPanel * C::TB;
+              const uint32_t o = so + m * kMatrix + j * (C::KS * kPanel * C::TB);
+              tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + xo + j * (C::KS * C::XB), acc[m]);
+            }
+          }
+        } else {
+          const uint32_t so = s * C::STAGE + ck * width * C::TB, xo = s * C::STAGE + ck * C::XB;
+#pragma unroll 1
+          for (int j = 0; j < C::T; j++) {                      // this warp's tile rows of the stage: ck, ck + KS, ...
+            if (ck + j * C::KS < n) {
+#pragma unroll
+              for (int m = 0; m < NW; m++) {
+                const uint32_t o = so + (m * RPS * C::UPS * kPanel + j * C::KS * width) * C::TB;
+                tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + xo + j * C::KS * C::XB, acc[m]);
+              }
             }
           }
         }
@@ -471,7 +485,7 @@ __global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_ke
 
 // ---- host side: pick a configuration, size shared memory, launch ----
 
-int g_wc[3] = {4, 8, 16};  // tile columns per sub-panel for 1, 2 and 4 token groups
+int g_wc[3] = {4, 4, 4};  // tile columns per sub-panel for 1, 2 and 4 token groups
 int g_stages = 0;          // 0: as many as fit
 unsigned long long *g_trace = nullptr;
 
