@@ -9,7 +9,7 @@
 // sub-panel that several CTAs share is finished by the CTA that holds its last tile row: the others write their
 // fp32 partial sums to scratch and bump a counter; the owner, which takes that sub-panel last, waits for the
 // counter (with a limit), adds the partials in CTA order, so results do not depend on timing, and runs the
-// epilogue. The launch is cooperative, so all CTAs are resident and the wait cannot starve.
+// epilogue. Contributors never wait, so the owner's wait always ends; it is bounded all the same.
 //
 // Inside a CTA: warp 16 is the producer. One of its lanes waits for a free stage and announces the stage's bytes
 // to the stage's mbarrier; then each lane issues one bulk copy (a run of weights, or a piece of an x tile). The 16 consumer
@@ -31,7 +31,7 @@ namespace {
 
 constexpr int kConsumerWarps = 16;
 constexpr int kMaxStages = 8;
-constexpr int kMaxCtas = 256;
+constexpr int kMaxCtas = 320;
 constexpr int kMaxSubPanels = 16384;
 constexpr uint32_t kSpinLimit = 1u << 14;   // attempts of up to 100 us each (mbarriers) or 64 ns polls x 32 (counters)
 constexpr int kSmemBudget = 225 * 1024;
@@ -64,9 +64,11 @@ struct GemvParams {
 
 template <int FMT, int NW, int TG, int WC>
 struct Config {
-  // Consumer warps. 16, except for the widest accumulators (32 rows of a gate/up pair), where 12 warps leave each
-  // thread 128 registers instead of 96.
-  static constexpr int CW = WC == 12 ? 12 : 16;
+  // Two CTAs of 8 consumer warps (plus the producer warp) share an SM, so that a CTA that is starting up, combining
+  // partial sums or belongs to the next launch overlaps with one that streams. The widest accumulators (32 rows of a
+  // gate/up pair) take one CTA of 12 warps per SM, which leaves each thread 128 registers.
+  static constexpr int OCC = WC == 12 ? 1 : 2;
+  static constexpr int CW = WC == 12 ? 12 : 8;
   static constexpr int THREADS = (CW + 1) * 32;
   static constexpr int KS = CW / WC;                             // k-slices: warps sharing a column
   static constexpr int T = NW == 2 ? 1 : (FMT == BT_BFP4 && TG == 1 ? 4 : 2);   // tile rows a warp takes per stage
@@ -242,7 +244,7 @@ __device__ __forceinline__ Segments segments_of(long long u0, long long u1, int 
 }
 
 template <int FMT, int NW, int TG, int WC>
-__global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), (Config<FMT, NW, TG, WC>::OCC)) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap xmap) {
   using C = Config<FMT, NW, TG, WC>;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -261,6 +263,9 @@ __global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_ke
   int *error = p.error;
 
   BT_TRACE(0, threadIdx.x == 0);
+  // The next launch in the stream may start as soon as there is room for its CTAs: what it does before its own
+  // griddepcontrol.wait (set up, prefetch weights) does not depend on this launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.nstages; s++) {
       mbar_init(full0 + 8 * s, 1);
@@ -279,10 +284,27 @@ __global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_ke
     constexpr int RPS = WC / kPanel;             // runs of the streamed layout in a sub-panel
     int s = 0;                 // the stage to fill next
     uint32_t round = 0;        // how many times the ring has wrapped
+    // Weights never depend on the launch before this one, x (the previous layer's result) does. So the first pass
+    // over the ring issues only the weight copies and notes the x copies; then the warp waits for the previous launch
+    // to finish (griddepcontrol.wait) and issues the noted x copies. From there on a stage gets both at once.
+    bool released = false;
+    int noted = 0, noted_kt[kMaxStages], noted_n[kMaxStages];
+    auto copy_x = [&](int stage_index, int kt, int n) {
+      const uint32_t bar = full0 + 8 * stage_index, xs = sbase + kStageBase + stage_index * C::STAGE + C::W_BYTES;
+      if (TG == 4) bulk_g2s(xs, p.x + (size_t)kt * 2048, n * 2048, bar);
+      else tma_load_3d(xs, &xmap, 0, 0, kt, bar);   // tiles past the last read as zeros
+    };
+    auto release = [&]() {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (lane == NW * RPS)
+        for (int i = 0; i < noted; i++) copy_x(i, noted_kt[i], noted_n[i]);
+      released = true;
+    };
     for (int q = 0; q < seg.n; q++) {
       int sp = (int)(seg.a[q] / KT), kt = (int)(seg.a[q] % KT);
       for (int left = (int)(seg.b[q] - seg.a[q]); left > 0;) {
         const int n = min(min(C::UPS, left), KT - kt);
+        if (!released && round > 0) release();
         const uint32_t bar = full0 + 8 * s, stage = sbase + kStageBase + s * C::STAGE;
         if (lane == 0) {
           if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, kSpinLimit)) atomicExch(error, 1);
@@ -294,15 +316,18 @@ __global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), 1) gemv_ke
           if (width > 0)
             bulk_g2s(stage + (m * RPS + r) * C::UPS * kPanel * C::TB, p.w[m] + ((size_t)run * kPanel * KT + (size_t)kt * width) * C::TB,
                      n * width * C::TB, bar);
-        } else if (lane == NW * RPS) {
-          if (TG == 4) bulk_g2s(stage + C::W_BYTES, p.x + (size_t)kt * 2048, n * 2048, bar);
-          else tma_load_3d(stage + C::W_BYTES, &xmap, 0, 0, kt, bar);   // tiles past the last read as zeros
+        }
+        if (released) {
+          if (lane == NW * RPS) copy_x(s, kt, n);
+        } else {
+          noted_kt[noted] = kt, noted_n[noted] = n, noted++;
         }
         left -= n, kt += n;
         if (kt == KT) kt = 0, sp++;
         if (++s == p.nstages) s = 0, round++;
       }
     }
+    if (!released) release();
     BT_TRACE(5, lane == 0);
     return;
   }
@@ -493,7 +518,8 @@ template <int FMT, int NW, int TG, int WC>
 int launch(const GemvParams &base, int sms, cudaStream_t stream) {
   using C = Config<FMT, NW, TG, WC>;
   GemvParams p = base;
-  int fit = (kSmemBudget - (C::FIXED + 127) / 128 * 128) / C::STAGE;
+  constexpr int kBudget = kSmemBudget / C::OCC - (C::OCC > 1 ? 1024 : 0);     // the runtime keeps 1 KiB per resident CTA
+  int fit = (kBudget - (C::FIXED + 127) / 128 * 128) / C::STAGE;
   p.nstages = min(kMaxStages, g_stages > 0 ? min(g_stages, fit) : fit);
   if (p.nstages < 2) return fail(BT_DEVICE, "bt_gemv_bfp: a stage of %d bytes leaves room for %d stages", C::STAGE, p.nstages);
   const int smem = (C::FIXED + 127) / 128 * 128 + p.nstages * C::STAGE;
@@ -501,11 +527,11 @@ int launch(const GemvParams &base, int sms, cudaStream_t stream) {
   int device = 0;
   BT_CUDA(cudaGetDevice(&device));
   if (!configured[device & 63]) {
-    BT_CUDA(cudaFuncSetAttribute(gemv_kernel<FMT, NW, TG, WC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    BT_CUDA(cudaFuncSetAttribute(gemv_kernel<FMT, NW, TG, WC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBudget));
     configured[device & 63] = true;
   }
   const long long units = (long long)((p.TC + WC - 1) / WC) * p.KT;
-  const int ctas = (int)min((long long)min(sms, kMaxCtas), units);
+  const int ctas = (int)min((long long)min(sms * C::OCC, kMaxCtas), units);
   // x as (8 TG rows x 32 bytes, 2 faces, K tiles): a box picks the rows the MMAs read out of UPS consecutive tiles
   alignas(64) CUtensorMap xmap;
   memset(&xmap, 0, sizeof xmap);
@@ -514,8 +540,15 @@ int launch(const GemvParams &base, int sms, cudaStream_t stream) {
     const uint32_t box[3] = {(uint32_t)(64 * TG), 2, (uint32_t)C::UPS};
     if (int st = make_tmap(&xmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return st;
   }
-  void *args[2] = {&p, &xmap};
-  BT_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(gemv_kernel<FMT, NW, TG, WC>), dim3(ctas), dim3(C::THREADS), args, smem, stream));
+  // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
+  // It only sets up and prefetches weights until its producer warps pass griddepcontrol.wait.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(C::THREADS), cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  BT_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, NW, TG, WC>, p, xmap));
   return launched("gemv_kernel");
 }
 
@@ -524,9 +557,8 @@ int launch_wc(const GemvParams &p, int wc, int sms, cudaStream_t stream) {
   if constexpr (NW == 2 && TG == 4) {
     return launch<FMT, NW, TG, 12>(p, sms, stream);   // the widest accumulators: see Config::CW
   } else {
-    if (wc == 4) return launch<FMT, NW, TG, 4>(p, sms, stream);
     if (wc == 8) return launch<FMT, NW, TG, 8>(p, sms, stream);
-    return launch<FMT, NW, TG, 16>(p, sms, stream);
+    return launch<FMT, NW, TG, 4>(p, sms, stream);
   }
 }
 
@@ -570,7 +602,7 @@ int bt_gemv_workspace_bytes(int device, size_t *bytes) {
 int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages) {
   const int wc[3] = {wc_m8, wc_m16, wc_m32};
   for (int i = 0; i < 3; i++) {
-    BT_REQUIRE(wc[i] == 0 || wc[i] == 4 || wc[i] == 8 || wc[i] == 16, "bt_gemv_tune: sub-panel width must be 4, 8 or 16, not %d", wc[i]);
+    BT_REQUIRE(wc[i] == 0 || wc[i] == 4 || wc[i] == 8, "bt_gemv_tune: sub-panel width must be 4 or 8, not %d", wc[i]);
     if (wc[i]) g_wc[i] = wc[i];
   }
   BT_REQUIRE(stages >= 0 && stages <= kMaxStages, "bt_gemv_tune: stages must be 0..%d", kMaxStages);
