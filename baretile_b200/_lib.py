@@ -15,6 +15,12 @@ class DeviceInfo(ctypes.Structure):
               ("memory_bytes", u64), ("max_shared_bytes", i32), ("clock_khz", i32)]
 
 
+class GemvOp(ctypes.Structure):
+  """bt_gemv_op: one matmul of a bt_gemv_queue call; the fields are bt_gemv_bfp's arguments of the same names."""
+  _fields_ = [("fmt", i32), ("epilogue", i32), ("M", i32), ("K", i32), ("N", i32), ("out_dtype", i32), ("arg_base", i32), ("alpha", f32),
+              ("x", u64), ("w", u64), ("w2", u64), ("add", u64), ("out", u64), ("arg_val", u64), ("arg_idx", u64)]
+
+
 SIGNATURES = {
   "bt_device_count": [ctypes.POINTER(i32)],
   "bt_device_info_get": [i32, ctypes.POINTER(DeviceInfo)],
@@ -49,7 +55,7 @@ SIGNATURES = {
   "bt_gemm_bfp": [i32, i32, i32, i32, i32, i32, u64, u64, u64, f32, u64, i32, u64, u64],
   "bt_gemv_bfp_static": [i32, i32, i32, i32, i32, i32, u64, u64, u64, u64, f32, u64, i32, u64, u64, i32, u64],
   "bt_gemv_check": [i32, u64, u64, ctypes.POINTER(i32)],
-  "bt_gemv_tune": [i32, i32, i32, i32],
+  "bt_gemv_queue": [i32, i32, ctypes.POINTER(GemvOp), u64, size_t, u64],
   "bt_gemv_trace": [u64],
   "bt_launch_count": [ctypes.POINTER(u64)],
 }

@@ -1,51 +1,101 @@
-// Decode matmul for up to 32 token rows: out = epilogue(alpha * x @ W + add), W block-float in streaming layout.
+// Decode matmul for up to 32 token rows: out = epilogue(alpha * x @ W + add), W block-float in streaming layout,
+// and a queue of such matmuls run by ONE launch.
 //
-// The kernel is bound by HBM: every packed weight byte is read once, by a bulk (TMA) copy into a ring of
+// The work is bound by HBM: every packed weight byte is read once, by a bulk (TMA) copy into a ring of
 // shared-memory stages, and dequantised in registers on its way into a bf16 MMA with fp32 accumulators.
 //
-// Decomposition ("stream-K"). The weight matrix is cut into sub-panels of WC tile columns. A unit is one tile
-// row of one sub-panel (WC tiles). Units are numbered sub-panel by sub-panel and dealt out in equal contiguous
-// ranges to one persistent CTA per SM, so every SM streams the same number of bytes whatever the shape. A
-// sub-panel that several CTAs share is finished by the CTA that holds its last tile row: the others write their
-// fp32 partial sums to scratch and bump a counter; the owner, which takes that sub-panel last, waits for the
+// A queue. In decode one matmul's result is the next one's x, so between two of them the GPU has nothing to read
+// unless the next weights are already on their way. The kernel therefore takes a list of matmuls (up to kQueueMax
+// per launch) and runs them in order with the same persistent CTAs. The producer warp of a CTA walks the whole
+// list: weight copies depend on nothing and go out as soon as the ring has room, across the boundary between two
+// matmuls. Only the consumers wait: they read x straight from global memory (L2), and not before every CTA has
+// reported the previous matmul finished (a counter per matmul in global memory, read with acquire semantics).
+// While that report travels, the ring fills with the next weights.
+//
+// Decomposition ("stream-K"). A weight matrix is cut into sub-panels of 4 tile columns (one run of the streaming
+// layout). A unit is one tile row of one sub-panel. Units are numbered sub-panel by sub-panel and dealt out in
+// equal contiguous ranges to the CTAs (two per SM), so every SM streams the same number of bytes whatever the
+// shape. A sub-panel that several CTAs share is finished by the CTA that holds its last tile row: the others write
+// their fp32 partial sums to scratch and bump a counter; the owner, which takes that sub-panel last, waits for the
 // counter (with a limit), adds the partials in CTA order, so results do not depend on timing, and runs the
 // epilogue. Contributors never wait, so the owner's wait always ends; it is bounded all the same.
 //
-// Inside a CTA: warp 16 is the producer. One of its lanes waits for a free stage and announces the stage's bytes
-// to the stage's mbarrier; then each lane issues one bulk copy (a run of weights, or a piece of an x tile). The 16 consumer
-// warps form a WC x KS grid: warp (ck, cc) takes column cc of the sub-panel and every KS-th tile row of the
-// stage, so x tiles in shared memory serve WC warps. A weight tile is four 16x16 faces; a face is one
-// m16n8k16 MMA with the face's 16 output channels as the MMA's rows, 16 input channels as its K and up to 8
-// tokens as its columns. The 16 weights of a face row share an exponent e: the lane builds bf16 lanes
-// (sign << 15 | magnitude), i.e. +-q * 2^-133 as a bf16 subnormal, and multiplies by 2^(e - 64) as a packed bf16
-// multiply, which gives q * 2^(e - 133) * 2^-64 exactly; the epilogue multiplies the sums by 2^64.
+// Inside a CTA: warp 8 is the producer. It waits for room in the ring, announces the stage's bytes to the stage's
+// mbarrier and issues one bulk copy per weight matrix. Stages are as large as the matmul's kind wants and follow
+// one another through the ring's bytes; 16 mbarrier pairs go round with them. The 8 consumer
+// warps form a 2 x 4 grid: warp (ck, cc) takes column cc of the sub-panel; for one weight matrix ck picks every
+// other tile row of the stage (the two halves are added through shared memory when the sub-panel ends), for a
+// gate/up pair ck picks the matrix (the up half is handed to the gate warp for the epilogue). A weight tile is
+// four 16x16 faces; a face is one m16n8k16 MMA with the face's 16 output channels as the MMA's rows, 16 input
+// channels as its K and up to 8 tokens as its columns. The 16 weights of a face row share an exponent e: the lane
+// builds bf16 lanes (sign << 15 | magnitude), i.e. +-q * 2^-133 as a bf16 subnormal, and multiplies by 2^(e - 64)
+// as a packed bf16 multiply, which gives q * 2^(e - 133) * 2^-64 exactly; the epilogue multiplies the sums by 2^64.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "stream_layout.cuh"
-#include "tmap.cuh"
 #include <cstring>
 
 using namespace bt;
 
 namespace {
 
-constexpr int kConsumerWarps = 16;
-constexpr int kMaxStages = 8;
+constexpr int kWC = kPanel;                 // tile columns of a sub-panel = one run of the streaming layout
+constexpr int kCW = 8;                      // consumer warps per CTA
+constexpr int kThreads = (kCW + 2) * 32;    // plus the two producer warps
+constexpr int kOcc = 2;                     // CTAs per SM
+constexpr int kBars = 16;                   // stages in the ring at most: mbarriers that go round with the stages
 constexpr int kMaxCtas = 320;
 constexpr int kMaxSubPanels = 16384;
-constexpr uint32_t kSpinLimit = 1u << 14;   // attempts of up to 100 us each (mbarriers) or 64 ns polls x 32 (counters)
-constexpr int kSmemBudget = 225 * 1024;
+constexpr int kQueueMax = 32;               // matmuls per launch; longer lists take several launches
+constexpr uint32_t kSpinLimit = 1u << 14;   // attempts of up to 100 us each (mbarriers) or 32-64 ns polls x 32 (counters)
+
+// Shared memory of a CTA.
+constexpr int kSmFull = 0, kSmXFull = 128, kSmEmpty = 256;  // mbarriers: a stage's weights landed, its x landed, it is free again
+constexpr int kSmHeld = 384;                // uint32[2][kBars]: ring bytes of each stage in the ring, as each producer warp noted them
+constexpr int kSmArgVal = 512;              // float[4][32]: best value per column warp and token
+constexpr int kSmArgIdx = 512 + 512;        // int[4][32]: and its channel
+constexpr int kSmRed = 1536;                // 4 KiB: 8 accumulators per lane handed from warps ck = 1 to warps ck = 0
+constexpr int kSmRing = kSmRed + 4096;
+constexpr int kSmemBytes = (228 * 1024 / kOcc - 1024) / 128 * 128;   // an SM's shared memory less the runtime's 1 KiB per CTA
+constexpr int kRingBytes = kSmemBytes - kSmRing;
+static_assert(kSmRing % 128 == 0 && kRingBytes % 128 == 0, "stages are 128-byte aligned");
 
 // Scratch layout (byte offsets into the caller's workspace).
 constexpr size_t kWsError = 0;                                   // int: set to nonzero when a wait gave up
 constexpr size_t kWsPanelsDone = 4;                              // int: sub-panels finished (argmax epilogue)
+constexpr size_t kWsOpsDone = 8;                                 // int[kQueueMax]: CTAs that finished each matmul of the launch
 constexpr size_t kWsCounters = 256;                              // int[kMaxSubPanels]: CTAs arrived at a sub-panel
 constexpr size_t kWsArgVal = kWsCounters + 4 * kMaxSubPanels;    // float[kMaxSubPanels][32]
 constexpr size_t kWsArgIdx = kWsArgVal + 4 * 32 * kMaxSubPanels; // int[kMaxSubPanels][32]
 constexpr size_t kWsPartials = kWsArgIdx + 4 * 32 * kMaxSubPanels;
-constexpr size_t kSlotFloatsMax = 2 * 16 * 2 * 4 * 4 * 32;       // NW * WC * 2 * TG * 4 * 32 at its largest
+constexpr size_t kSlotFloatsMax = 8 * 32 * 32;                   // 8 warps x up to 32 accumulators x 32 lanes
 constexpr size_t kWsBytes = kWsPartials + (size_t)kMaxCtas * kSlotFloatsMax * 4;
 
+// The shape of a stage for one kind of matmul: format, one matrix or a gate/up pair, token groups of 8 rows.
+struct Geometry {
+  int tb;        // bytes of a packed tile
+  int t;         // tile rows a warp takes per stage
+  int ups;       // units (tile rows) per stage
+  int matrix;    // bytes of one matrix's part of a stage
+  int w_bytes;   // all weights of a stage; the x tiles follow
+  int xb;        // bytes of an x tile (staged whole)
+  int stage;     // bytes of a stage
+};
+__host__ __device__ constexpr int stage_rows_per_warp(int fmt, int tg) { return tg == 4 ? 1 : 2; }
+__host__ __device__ constexpr Geometry geometry(int fmt, bool pair, int tg) {
+  Geometry g{};
+  g.tb = tile_bytes(fmt), g.t = stage_rows_per_warp(fmt, tg);
+  g.ups = pair ? g.t : 2 * g.t;
+  g.matrix = g.ups * kWC * g.tb;
+  g.w_bytes = (pair ? 2 : 1) * g.matrix;
+  g.xb = 2048;
+  g.stage = g.w_bytes + g.ups * g.xb;
+  return g;
+}
+static_assert(geometry(BT_BFP8, false, 1).stage % 128 == 0 && geometry(BT_BFP4, false, 4).stage % 128 == 0 && geometry(BT_BFP4, true, 4).stage % 128 == 0,
+              "stages keep the ring 128-byte aligned");
+
+// One matmul of the queue, as the kernel sees it.
 struct GemvParams {
   const uint8_t *x;
   const uint8_t *w[2];
@@ -53,36 +103,22 @@ struct GemvParams {
   void *out;
   float *arg_val;
   int *arg_idx;
-  // scratch, zero before first use: a wait-gave-up flag, sub-panels finished (argmax), CTAs arrived per sub-panel,
-  // per-sub-panel argmax candidates, and one slot of partial sums per CTA
-  int *error, *panels_done, *counters, *part_idx;
-  float *part_val, *partials;
-  float alpha;
-  int arg_base, M, KT, TC, epi, out_fp32, nstages;
   unsigned long long *trace;  // when set: 8 timestamps per CTA (debugging aid)
+  float alpha;
+  int arg_base, M, KT, TC, epi, out_fp32;
+  int fmt, pair, tg;
 };
 
-template <int FMT, int NW, int TG, int WC>
-struct Config {
-  // Two CTAs of 8 consumer warps (plus the producer warp) share an SM, so that a CTA that is starting up, combining
-  // partial sums or belongs to the next launch overlaps with one that streams. The widest accumulators (32 rows of a
-  // gate/up pair) take one CTA of 12 warps per SM, which leaves each thread 128 registers.
-  static constexpr int OCC = WC == 12 ? 1 : 2;
-  static constexpr int CW = WC == 12 ? 12 : 8;
-  static constexpr int THREADS = (CW + 1) * 32;
-  static constexpr int KS = CW / WC;                             // k-slices: warps sharing a column
-  static constexpr int T = NW == 2 ? 1 : (FMT == BT_BFP4 && TG == 1 ? 4 : 2);   // tile rows a warp takes per stage
-  static constexpr int UPS = KS * T;                             // units (tile rows) per stage
-  static constexpr int TB = tile_bytes(FMT);
-  static constexpr int XB = TG == 1 ? 512 : TG == 2 ? 1024 : 2048;  // bytes of an x tile staged: rows 0-7, 0-15 or all 32
-  static constexpr int W_BYTES = UPS * NW * WC * TB;
-  static constexpr int STAGE = (W_BYTES + UPS * XB + 127) / 128 * 128;
-  static constexpr int ACC = NW * 2 * TG * 4;                    // accumulator floats per lane
-  static constexpr int SLAB = WC * ACC * 32 * 4;                 // one k-slice's accumulators, all columns
-  static constexpr int RED_SLABS = KS > 1 ? (24576 / SLAB < 1 ? 1 : 24576 / SLAB < KS - 1 ? 24576 / SLAB : KS - 1) : 0;
-  static constexpr int RED = RED_SLABS * SLAB;                   // cross-warp reduction buffer
-  static constexpr int FIXED = 4352 + RED;                       // barriers, flags, argmax staging, reduction buffer
-  static constexpr size_t SLOT = (size_t)WC * ACC * 32;          // floats in one partial slot
+// What one launch gets: the matmuls and the scratch they share. The scratch holds a
+// wait-gave-up flag, the counts of finished sub-panels (argmax) and finished matmuls, the arrivals per sub-panel
+// (all zero before first use; the kernel leaves them zero), per-sub-panel argmax candidates and one slot of partial
+// sums per CTA.
+struct Queue {
+  int n;
+  int *error, *panels_done, *ops_done, *counters, *part_idx;
+  float *part_val, *partials;
+  int slot_floats;            // floats between two CTAs' slots of partial sums
+  GemvParams op[kQueueMax];
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -92,11 +128,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 #ifdef BT_GEMV_TRACE
 #define BT_TRACE(slot, cond) do { if (p.trace && (cond)) p.trace[blockIdx.x * 8 + (slot)] = global_ns(); } while (0)
+// CTA 0 also stamps its first 64 stages of a matmul: stage wait over / copies issued (producer), data there /
+// stage consumed (consumer thread 0), at 2400 + 4 * stage + which
+#define BT_STAGE_TRACE(which, stage, cond) do { if (p.trace && blockIdx.x == 0 && (stage) < 32 && (cond)) p.trace[2400 + 8 * (stage) + (which)] = clock64(); } while (0)
 #else
 #define BT_TRACE(slot, cond) do { } while (0)
+#define BT_STAGE_TRACE(which, stage, cond) do { } while (0)
 #endif
 
-__device__ __forceinline__ long long range_start(long long units, int b, int ctas) { return units * b / ctas; }
+__host__ __device__ __forceinline__ long long range_start(long long units, int b, int ctas) { return units * b / ctas; }
+// The CTA whose (non-empty) range holds unit u.
 __device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
   int b = (int)(u * ctas / units);
   while (b + 1 < ctas && range_start(units, b + 1, ctas) <= u) b++;
@@ -110,22 +151,25 @@ __device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
   return prmt(ew, 0u, HI ? 0x4342u : 0x4140u) * 128u + 0x1F801F80u;
 }
 
-// One weight tile times the staged x tile, added into acc[ng][tg][4]. `tile` and `xs` are shared-memory addresses
-// that already include the lane's own offsets: tile = tile base + 16 * lane; xs = x tile base + 32 * g + 8 * t
-// (g = lane / 4, t = lane % 4); `ex` = tile base + 16 * t, where the lane's exponents are.
+// One weight tile times the staged x tile, added into acc[ng][tg][4]. `tile`, `ex` and `xs` are shared-memory
+// addresses that already include the lane's own offsets: tile = tile base + 16 * lane; ex = tile base + 16 * t,
+// where the lane's exponents are; xs = x tile base + 32 * g + 8 * t (g = lane / 4, t = lane % 4).
 template <int FMT, int TG>
 __device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t ex, uint32_t xs, float (&acc)[2][TG][4]) {
+#ifdef BT_NO_MATH
+  return;
+#endif
   const uint4 ev = lds128(ex);
   const uint32_t ee[4] = {ev.x, ev.y, ev.z, ev.w};
-  uint4 wv[2];
-  if (FMT == BT_BFP8) wv[0] = lds128(tile + 64), wv[1] = lds128(tile + 64 + 512);
-  else wv[0] = lds128(tile + 64), wv[1] = wv[0];
   uint2 bx[2][TG];
 #pragma unroll
   for (int h = 0; h < 2; h++) {
 #pragma unroll
-    for (int tg = 0; tg < TG; tg++) bx[h][tg] = lds64(xs + (TG == 1 ? h * 256 : (tg >> 1) * 1024 + h * 512 + (tg & 1) * 256));
+    for (int tg = 0; tg < TG; tg++) bx[h][tg] = lds64(xs + (tg >> 1) * 1024 + h * 512 + (tg & 1) * 256);
   }
+  uint4 wv[2];
+  if (FMT == BT_BFP8) wv[0] = lds128(tile + 64), wv[1] = lds128(tile + 64 + 512);
+  else wv[0] = lds128(tile + 64), wv[1] = wv[0];
 #pragma unroll
   for (int h = 0; h < 2; h++) {
 #pragma unroll
@@ -156,10 +200,11 @@ __device__ __forceinline__ bool beats(float av, int ai, float bv, int bi) { retu
 
 
 // The epilogue of one finished tile column. Lane (g, t) holds, for each channel group ng and token group tg,
-// tokens 8 tg + 2t + j (j = 0, 1) and channels 16 ng + 2g + {0, 1}: acc[..][ng][tg][j] and [2 + j].
-template <int NW, int TG>
-__device__ __forceinline__ void finish_column(const GemvParams &p, const float (&acc)[NW][2][TG][4], int col, int cc, int lane,
-                                              float *arg_v, int *arg_i) {
+// tokens 8 tg + 2t + j (j = 0, 1) and channels 16 ng + 2g + {0, 1}: acc[ng][tg][j] and [2 + j].
+// For a gate/up pair `acc` holds the gate sums and `up` the up sums in the same arrangement.
+template <int TG, bool PAIR>
+__device__ __forceinline__ void finish_column(const GemvParams &p, const float (&acc)[2][TG][4], const float (&up)[2][TG][4], int col, int cc,
+                                              int lane, float *arg_v, int *arg_i) {
   const int g = lane >> 2, t = lane & 3;
   const float unscale = 18446744073709551616.f * p.alpha;  // 2^64: the weights entered the MMA scaled by 2^-64
   float best_v[TG][2];
@@ -176,14 +221,14 @@ __device__ __forceinline__ void finish_column(const GemvParams &p, const float (
       for (int j = 0; j < 2; j++) {
         const int m = 8 * tg + 2 * t + j, at = ((m >> 4) * 2 + ng) * 256 + (m & 15) * 16 + 2 * g;
         const bool valid = p.M == 1 || (tg <= kLast && m < p.M);
-        float v0 = acc[0][ng][tgs][j] * unscale, v1 = acc[0][ng][tgs][2 + j] * unscale;
+        float v0 = acc[ng][tgs][j] * unscale, v1 = acc[ng][tgs][2 + j] * unscale;
         if (p.add) {
           const uint32_t a = *reinterpret_cast<const uint32_t *>(p.add + (size_t)col * 1024 + at);
           v0 += bf16_value((uint16_t)a), v1 += bf16_value((uint16_t)(a >> 16));
         }
         if (p.epi == BT_EPI_RELU) v0 = fmaxf(v0, 0.f), v1 = fmaxf(v1, 0.f);
         else if (p.epi == BT_EPI_SILU) v0 = silu(v0), v1 = silu(v1);
-        else if (NW == 2) v0 = silu(v0) * (acc[NW - 1][ng][tgs][j] * unscale), v1 = silu(v1) * (acc[NW - 1][ng][tgs][2 + j] * unscale);
+        else if (PAIR) v0 = silu(v0) * (up[ng][tgs][j] * unscale), v1 = silu(v1) * (up[ng][tgs][2 + j] * unscale);
         if (p.epi == BT_EPI_ARGMAX) {
           if (tg <= kLast && m < p.M) {
             const int n0 = col * 32 + 16 * ng + 2 * g;
@@ -243,330 +288,447 @@ __device__ __forceinline__ Segments segments_of(long long u0, long long u1, int 
   return s;
 }
 
-template <int FMT, int NW, int TG, int WC>
-__global__ void __launch_bounds__((Config<FMT, NW, TG, WC>::THREADS), (Config<FMT, NW, TG, WC>::OCC)) gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap xmap) {
-  using C = Config<FMT, NW, TG, WC>;
-  extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t sbase = smem_u32(smem);
-  const uint32_t full0 = sbase, empty0 = sbase + 64;
-  int *flags = reinterpret_cast<int *>(smem + 128);               // [0], [1]: last-arriver verdicts
-  float *arg_v = reinterpret_cast<float *>(smem + 256);           // [16][32] best value per column warp and token
-  int *arg_i = reinterpret_cast<int *>(smem + 256 + 2048);        // [16][32] and its channel
-  float *red = reinterpret_cast<float *>(smem + 4352);
-  constexpr int kStageBase = (C::FIXED + 127) / 128 * 128;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ctas = gridDim.x, cta = blockIdx.x, KT = p.KT;
-  const int subpanels = (p.TC + WC - 1) / WC;
-  const long long units = (long long)subpanels * KT;
-  const long long u0 = range_start(units, cta, ctas), u1 = range_start(units, cta + 1, ctas);
-  const Segments seg = segments_of(u0, u1, KT);
-  int *error = p.error;
-
-  BT_TRACE(0, threadIdx.x == 0);
-  // The next launch in the stream may start as soon as there is room for its CTAs: what it does before its own
-  // griddepcontrol.wait (set up, prefetch weights) does not depend on this launch.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.nstages; s++) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, C::CW);
-    }
-    mbar_fence_init();
+// The ring position both sides of a CTA keep: the next stage and how many times the ring has wrapped.
+// Where the next stage goes, kept in step by both sides of a CTA: stages follow one another through the ring's
+// bytes (a stage that would run past the end starts over at 0) and through the kBars mbarrier pairs.
+struct Ring {
+  uint32_t count;   // stages placed so far
+  uint32_t off;     // where the next one would start
+  __device__ __forceinline__ uint32_t place(uint32_t bytes) {       // byte offset of the next stage
+    if (off + bytes > kRingBytes) off = 0;
+    const uint32_t at = off;
+    off += bytes;
+    return at;
   }
-  __syncthreads();
-  BT_TRACE(1, threadIdx.x == 0);
+  __device__ __forceinline__ uint32_t bar() const { return 8 * (count % kBars); }        // its mbarriers' offset
+  __device__ __forceinline__ uint32_t parity() const { return (count / kBars) & 1; }    // and the phase to wait for
+};
 
-  if (warp == C::CW) {
-    // ---- producer: lane 0 waits for the stage to be free and announces its bytes; then one lane per copy issues it.
-    // A bulk copy costs the issuing warp on the order of a hundred cycles whatever its size, so a stage is a few
-    // large copies: one per run of weights, and one for the stage's x tiles (a tiled TMA box that picks the rows
-    // the MMAs need out of each tile, or for 32 rows the tiles as they are).
-    constexpr int RPS = WC / kPanel;             // runs of the streamed layout in a sub-panel
-    int s = 0;                 // the stage to fill next
-    uint32_t round = 0;        // how many times the ring has wrapped
-    // Weights never depend on the launch before this one, x (the previous layer's result) does. So the first pass
-    // over the ring issues only the weight copies and notes the x copies; then the warp waits for the previous launch
-    // to finish (griddepcontrol.wait) and issues the noted x copies. From there on a stage gets both at once.
-    bool released = false;
-    int noted = 0, noted_kt[kMaxStages], noted_n[kMaxStages];
-    auto copy_x = [&](int stage_index, int kt, int n) {
-      const uint32_t bar = full0 + 8 * stage_index, xs = sbase + kStageBase + stage_index * C::STAGE + C::W_BYTES;
-      if (TG == 4) bulk_g2s(xs, p.x + (size_t)kt * 2048, n * 2048, bar);
-      else tma_load_3d(xs, &xmap, 0, 0, kt, bar);   // tiles past the last read as zeros
-    };
-    auto release = [&]() {
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      if (lane == NW * RPS)
-        for (int i = 0; i < noted; i++) copy_x(i, noted_kt[i], noted_n[i]);
-      released = true;
-    };
-    for (int q = 0; q < seg.n; q++) {
-      int sp = (int)(seg.a[q] / KT), kt = (int)(seg.a[q] % KT);
-      for (int left = (int)(seg.b[q] - seg.a[q]); left > 0;) {
-        const int n = min(min(C::UPS, left), KT - kt);
-        if (!released && round > 0) release();
-        const uint32_t bar = full0 + 8 * s, stage = sbase + kStageBase + s * C::STAGE;
-        if (lane == 0) {
-          if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, kSpinLimit)) atomicExch(error, 1);
-          mbar_expect_tx(bar, n * NW * min(WC, p.TC - sp * WC) * C::TB + (TG == 4 ? n : C::UPS) * C::XB);
+// A CTA's stages of one matmul, in order: sub-panel, first tile row and number of tile rows of each.
+struct Walk {
+  Segments seg;
+  int KT, ups, sq, sp, kt, left;
+  __device__ __forceinline__ void start(const Segments &s, int kt_count, int units_per_stage) {
+    seg = s, KT = kt_count, ups = units_per_stage, sq = 0;
+    if (seg.n > 0) sp = (int)(seg.a[0] / KT), kt = (int)(seg.a[0] % KT), left = (int)(seg.b[0] - seg.a[0]);
+  }
+  __device__ __forceinline__ bool more() const { return sq < seg.n; }
+  __device__ __forceinline__ int rows() const { return min(min(ups, left), KT - kt); }
+  // this stage ends its sub-panel's share of the range
+  __device__ __forceinline__ bool ends_piece() const { return left == rows() || kt + rows() == KT; }
+  __device__ __forceinline__ void next() {
+    const int n = rows();
+    left -= n, kt += n;
+    if (kt == KT) kt = 0, sp++;
+    if (left == 0 && ++sq < seg.n) sp = (int)(seg.a[sq] / KT), kt = (int)(seg.a[sq] % KT), left = (int)(seg.b[sq] - seg.a[sq]);
+  }
+};
+
+// ---- producers: two warps walk the whole queue ---------------------------------------------------------------
+// Warp 8 copies weights, warp 9 copies x. Both follow the same stages through the ring and wait for the same room
+// (the oldest stage in the ring freed by the consumers), each keeping its own books, so neither waits for the other.
+// Weights never depend on an earlier matmul: their copies go out as soon as the ring has room, lane 0 announcing
+// the bytes and lanes 0 and 1 issuing one bulk copy per weight matrix. x is the result of an earlier matmul: the x
+// warp waits (with a limit) until every CTA has reported the matmul before finished, then copies each stage's x
+// tiles with one bulk copy (an asynchronous copy costs its issuer some 250 cycles whatever its size, so the tiles
+// go whole rather than row by row). While the x warp waits, the weight warp fills the ring.
+template <bool WEIGHTS>
+__device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t sbase, int cta, int ctas) {
+  const uint32_t full0 = sbase + kSmFull, xfull0 = sbase + kSmXFull, empty0 = sbase + kSmEmpty, ring0 = sbase + kSmRing;
+  volatile uint32_t *held = reinterpret_cast<volatile uint32_t *>(smem + kSmHeld) + (WEIGHTS ? 0 : kBars);   // ring bytes of each stage in the ring
+  const int lane = threadIdx.x & 31;
+  Ring ring{0, 0};
+  uint32_t oldest = 0, used = 0;        // first stage not yet known to be free; ring bytes held from there on
+  for (int i = 0; i < q.n; i++) {
+    const GemvParams &p = q.op[i];
+    const Geometry g = geometry(p.fmt, p.pair != 0, p.tg);
+    const int KT = p.KT, nw = p.pair ? 2 : 1;
+    const long long units = (long long)((p.TC + kWC - 1) / kWC) * KT;
+    const int active = (int)min((long long)ctas, units);     // a small matmul leaves the last CTAs without work
+    if (cta >= active) continue;
+    Walk walk;
+    walk.start(segments_of(range_start(units, cta, active), range_start(units, cta + 1, active), KT), KT, g.ups);
+    const uint8_t *w = p.w[lane < nw ? lane : 0];
+    bool gate = !WEIGHTS;                 // the x warp has yet to wait for the matmul before this one
+    for (int stage_no = 0; walk.more(); walk.next(), stage_no++) {
+      const int n = walk.rows(), sp = walk.sp, kt = walk.kt;
+      // room: the stage's bytes plus what is skipped when it starts over at the ring's beginning
+      const uint32_t need = g.stage + (ring.off + g.stage > kRingBytes ? kRingBytes - ring.off : 0);
+      for (uint32_t spins = 0; used + need > kRingBytes || ring.count - oldest == kBars;) {
+        int ok = 0;
+        if (lane == 0) ok = mbar_try_wait(empty0 + 8 * (oldest % kBars), (oldest / kBars) & 1, 100000u);
+        if (__shfl_sync(0xFFFFFFFFu, ok, 0)) {
+          used -= held[oldest % kBars], oldest++;
+        } else if (++spins > kSpinLimit) {
+          if (lane == 0) atomicExch(q.error, 1);
+          break;
         }
-        __syncwarp();
-        if (lane < NW * RPS) {
-          const int m = lane / RPS, r = lane % RPS, run = sp * RPS + r, width = min(kPanel, p.TC - run * kPanel);
-          if (width > 0)
-            bulk_g2s(stage + (m * RPS + r) * C::UPS * kPanel * C::TB, p.w[m] + ((size_t)run * kPanel * KT + (size_t)kt * width) * C::TB,
-                     n * width * C::TB, bar);
-        }
-        if (released) {
-          if (lane == NW * RPS) copy_x(s, kt, n);
-        } else {
-          noted_kt[noted] = kt, noted_n[noted] = n, noted++;
-        }
-        left -= n, kt += n;
-        if (kt == KT) kt = 0, sp++;
-        if (++s == p.nstages) s = 0, round++;
       }
-    }
-    if (!released) release();
-    BT_TRACE(5, lane == 0);
-    return;
-  }
-
-  // ---- consumers ----
-  const int ck = warp / WC, cc = warp % WC;
-  constexpr int RPS = WC / kPanel;
-  const int warp_tile = ((cc / kPanel) * C::UPS * kPanel + cc % kPanel) * C::TB;   // this warp's column inside a stage
-  float acc[NW][2][TG][4];
-// accumulator i of the lane, with i a compile-time constant after unrolling, so that acc stays in registers
-#define ACC_AT(i) acc[(i) / (8 * TG)][(i) / (4 * TG) % 2][(i) / 4 % TG][(i) % 4]
-#pragma unroll
-  for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
-
-  const int g = lane >> 2, tl = lane & 3;
-  // shared-memory addresses of this lane's pieces, relative to a stage: its 16 bytes of a tile's values, its exponents
-  // and its rows of an x tile
-  const uint32_t lane_tile = sbase + kStageBase + warp_tile + lane * 16, lane_ex = sbase + kStageBase + warp_tile + tl * 16;
-  const uint32_t lane_x = sbase + kStageBase + C::W_BYTES + g * 32 + tl * 8;
-  int s = 0;
-  uint32_t round = 0;
-  bool first_stage = true;
-  for (int q = 0; q < seg.n; q++) {
-    int sp = (int)(seg.a[q] / KT), kt = (int)(seg.a[q] % KT);
-    for (int left = (int)(seg.b[q] - seg.a[q]); left > 0;) {
-      const int n = min(min(C::UPS, left), KT - kt);
-      if (!mbar_wait(full0 + 8 * s, round & 1, kSpinLimit)) atomicExch(error, 2);
-      BT_TRACE(2, threadIdx.x == 0 && first_stage);
-      first_stage = false;
-      const int col = sp * WC + cc;
-      if (col < p.TC) {
-        const int width = min(kPanel, p.TC - (sp * RPS + cc / kPanel) * kPanel);   // tiles of a tile row in this run
-        if (n == C::UPS && width == kPanel) {
-          // a full stage of a full run: every offset is a compile-time constant
-          const uint32_t so = s * C::STAGE + ck * (kPanel * C::TB), xo = s * C::STAGE + ck * C::XB;
-#pragma unroll
-          for (int j = 0; j < C::T; j++) {
-#pragma unroll
-            for (int m = 0; m < NW; m++) {
-              constexpr int kMatrix = RPS * C::UPS * kPanel * C::TB;
-              const uint32_t o = so + m * kMatrix + j * (C::KS * kPanel * C::TB);
-              tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + xo + j * (C::KS * C::XB), acc[m]);
+      const uint32_t b = ring.count % kBars, stage = ring0 + ring.place(g.stage);
+      if (lane == 0) held[b] = need;
+      if (WEIGHTS) {
+        const int width = min(kWC, p.TC - sp * kWC);
+        const uint32_t bytes = n * width * g.tb;
+        BT_STAGE_TRACE(0, stage_no, lane == 0);
+        if (lane == 0) mbar_expect_tx(full0 + 8 * b, nw * bytes);
+        __syncwarp();
+        if (lane < nw) bulk_g2s(stage + lane * g.matrix, w + ((size_t)sp * kWC * KT + (size_t)kt * width) * g.tb, bytes, full0 + 8 * b);
+        BT_STAGE_TRACE(1, stage_no, lane == 0);
+      } else {
+        if (gate) {
+          // x is the result of the launch before this one, or of the matmul before this one
+          int ok = 1;
+          if (lane == 0) {
+            if (i == 0) {
+              asm volatile("griddepcontrol.wait;" ::: "memory");     // returns when the previous launch is complete and visible
+            } else {
+              uint32_t spins = 0;
+              while (ld_acquire_gpu(q.ops_done + i - 1) < ctas) {
+                if (++spins > kSpinLimit * 32) { ok = 0; break; }
+                __nanosleep(32);
+              }
             }
           }
-        } else {
-          const uint32_t so = s * C::STAGE + ck * width * C::TB, xo = s * C::STAGE + ck * C::XB;
-#pragma unroll 1
-          for (int j = 0; j < C::T; j++) {                      // this warp's tile rows of the stage: ck, ck + KS, ...
-            if (ck + j * C::KS < n) {
+          if (!__shfl_sync(0xFFFFFFFFu, ok, 0) && lane == 0) atomicExch(q.error, 5);
+          gate = false;
+          BT_TRACE(1, lane == 0);
+        }
+        BT_STAGE_TRACE(4, stage_no, lane == 0);
+        if (lane == 0) {
+          mbar_expect_tx(xfull0 + 8 * b, n * 2048);
+          bulk_g2s(stage + g.w_bytes, p.x + (size_t)kt * 2048, n * 2048, xfull0 + 8 * b);
+        }
+        BT_STAGE_TRACE(5, stage_no, lane == 0);
+        BT_STAGE_TRACE(6, stage_no, lane == 0);
+      }
+      used += need, ring.count++;
+      BT_STAGE_TRACE(7, stage_no, !WEIGHTS && lane == 0);
+    }
+    BT_TRACE(5, WEIGHTS && lane == 0);
+  }
+}
+
+// ---- consumers: one matmul of the queue -------------------------------------------------------------------------
+template <int FMT, int TG, bool PAIR>
+__device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Ring &ring, uint8_t *smem, uint32_t sbase, int cta, int ctas) {
+  constexpr Geometry G = geometry(FMT, PAIR, TG);
+  constexpr int ACC = 8 * TG;                                  // accumulator floats per lane
+  const uint32_t full0 = sbase + kSmFull, empty0 = sbase + kSmEmpty;
+  float *arg_v = reinterpret_cast<float *>(smem + kSmArgVal);
+  int *arg_i = reinterpret_cast<int *>(smem + kSmArgIdx);
+  float *red = reinterpret_cast<float *>(smem + kSmRed);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ck = warp >> 2, cc = warp & 3, tl = lane & 3;
+  const int KT = p.KT, subpanels = (p.TC + kWC - 1) / kWC;
+  const long long units = (long long)subpanels * KT;
+  const int active = (int)min((long long)ctas, units);       // a small matmul leaves the last CTAs without work
+  BT_TRACE(0, threadIdx.x == 0);
+  if (cta >= active) return;
+  Walk walk;
+  walk.start(segments_of(range_start(units, cta, active), range_start(units, cta + 1, active), KT), KT, G.ups);
+
+  float acc[2][TG][4];
+// accumulator i of the lane, with i a compile-time constant after unrolling, so that acc stays in registers
+#define ACC_OF(a, i) a[(i) / (4 * TG)][(i) / 4 % TG][(i) % 4]
 #pragma unroll
-              for (int m = 0; m < NW; m++) {
-                const uint32_t o = so + (m * RPS * C::UPS * kPanel + j * C::KS * width) * C::TB;
-                tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + xo + j * C::KS * C::XB, acc[m]);
-              }
+  for (int i = 0; i < ACC; i++) ACC_OF(acc, i) = 0.f;
+
+  // shared-memory addresses of this lane's pieces, relative to a stage: its 16 bytes of a tile's values, its exponents
+  // and its rows of an x tile
+  const uint32_t matrix0 = sbase + kSmRing + (PAIR ? ck * G.matrix : 0);
+  const uint32_t lane_tile = matrix0 + lane * 16, lane_ex = matrix0 + tl * 16, lane_x = sbase + kSmRing + G.w_bytes + lane * 8;
+  const bool mine = PAIR || ck == 0;       // this warp holds sums when a sub-panel ends
+  const int slab = PAIR ? warp : cc;       // and this is their place in a slot of partial sums
+  bool first_stage = true;
+  for (int stage_no = 0; walk.more(); stage_no++) {
+    const int n = walk.rows(), sp = walk.sp, col = sp * kWC + cc, done_sp = sp;
+    const bool piece_ends = walk.ends_piece();
+    walk.next();
+    const bool last_stage = !walk.more();
+    const uint32_t slot = ring.place(G.stage), bar = ring.bar();
+    {
+      if (!mbar_wait(full0 + bar, ring.parity(), kSpinLimit) || !mbar_wait(sbase + kSmXFull + bar, ring.parity(), kSpinLimit)) atomicExch(q.error, 2);
+      BT_STAGE_TRACE(2, stage_no, threadIdx.x == 0);
+      BT_TRACE(2, threadIdx.x == 0 && first_stage);
+      first_stage = false;
+      if (col < p.TC) {
+        const int width = min(kWC, p.TC - sp * kWC);
+        if (n == G.ups && width == kWC) {
+          // a full stage of a full run: every offset is a compile-time constant
+#pragma unroll
+          for (int j = 0; j < G.t; j++) {
+            const uint32_t row = PAIR ? j : 2 * j + ck, o = slot + (row * kWC + cc) * G.tb;
+            tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + slot + row * G.xb, acc);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < G.t; j++) {
+            const int row = PAIR ? j : 2 * j + ck;
+            if (row < n) {
+              const uint32_t o = slot + (row * width + cc) * G.tb;
+              tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + slot + row * G.xb, acc);
             }
           }
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * s);
-      if (++s == p.nstages) s = 0, round++;
-      left -= n, kt += n;
-      BT_TRACE(3, threadIdx.x == 0 && q == seg.n - 1 && left == 0);
-      if (left != 0 && kt != KT) continue;
-      const int done_sp = sp;
-      if (kt == KT) kt = 0, sp++;
+      if (lane == 0) mbar_arrive(empty0 + bar);
+      BT_STAGE_TRACE(3, stage_no, threadIdx.x == 0);
+      ring.count++;
+      BT_TRACE(3, threadIdx.x == 0 && last_stage);
+      if (!piece_ends) continue;
 
-      // ---- this CTA is done with sub-panel sp: reduce over k-slices, combine with other CTAs, run the epilogue ----
-      if (C::KS > 1) {
-        for (int r0 = 1; r0 < C::KS; r0 += C::RED_SLABS) {       // as many k-slices at a time as the buffer holds
-          if (ck >= r0 && ck < r0 + C::RED_SLABS) {
+      // ---- this CTA is done with sub-panel done_sp: add the k halves, combine with other CTAs, run the epilogue ----
+      if (!PAIR) {
+        // eight accumulators per lane at a time go through the 4 KiB buffer
 #pragma unroll
-            for (int i = 0; i < C::ACC; i++) red[(((ck - r0) * WC + cc) * C::ACC + i) * 32 + lane] = ACC_AT(i);
+        for (int r = 0; r < TG; r++) {
+          if (r > 0) named_barrier(1, kCW * 32);
+          if (ck == 1) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) red[(cc * 8 + i) * 32 + lane] = ACC_OF(acc, 8 * r + i);
           }
-          named_barrier(1, C::CW * 32);
+          named_barrier(1, kCW * 32);
           if (ck == 0) {
-            for (int r = r0; r < min(C::KS, r0 + C::RED_SLABS); r++) {
 #pragma unroll
-              for (int i = 0; i < C::ACC; i++) ACC_AT(i) += red[(((r - r0) * WC + cc) * C::ACC + i) * 32 + lane];
-            }
+            for (int i = 0; i < 8; i++) ACC_OF(acc, 8 * r + i) += red[(cc * 8 + i) * 32 + lane];
           }
-          if (r0 + C::RED_SLABS < C::KS) named_barrier(1, C::CW * 32);
         }
       }
-      BT_TRACE(6, threadIdx.x == 0 && q == seg.n - 1 && left == 0);
-      const int first = cta_of((long long)done_sp * KT, units, ctas), last = cta_of((long long)(done_sp + 1) * KT - 1, units, ctas);
+      BT_TRACE(6, threadIdx.x == 0 && last_stage);
+      const int first = cta_of((long long)done_sp * KT, units, active), last = cta_of((long long)(done_sp + 1) * KT - 1, units, active);
       const bool finish = cta == last;        // the owner finishes the sub-panel; the others only contribute
       if (first != last) {
-        float *partials = p.partials;
-        int *counter = p.counters + done_sp;
+        int *counter = q.counters + done_sp;
         if (!finish) {
           // a contributor has one shared sub-panel that it does not own, so one slot per CTA is enough
-          if (ck == 0) {
-            float4 *slot = reinterpret_cast<float4 *>(partials + (size_t)cta * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
+          if (mine) {
+            float4 *slot = reinterpret_cast<float4 *>(q.partials + (size_t)cta * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
 #pragma unroll
-            for (int i = 0; i < C::ACC / 4; i++)
-              slot[i * 32 + lane] = make_float4(ACC_AT(4 * i), ACC_AT(4 * i + 1), ACC_AT(4 * i + 2), ACC_AT(4 * i + 3));
+            for (int i = 0; i < ACC / 4; i++)
+              slot[i * 32 + lane] = make_float4(ACC_OF(acc, 4 * i), ACC_OF(acc, 4 * i + 1), ACC_OF(acc, 4 * i + 2), ACC_OF(acc, 4 * i + 3));
             __threadfence();
           }
-          named_barrier(1, C::CW * 32);
+          named_barrier(1, kCW * 32);
           if (threadIdx.x == 0) atomicAdd(counter, 1);
         } else {
           // wait, with a limit, until the last - first other contributors have signalled
           if (threadIdx.x == 0) {
             uint32_t spins = 0;
             while (*reinterpret_cast<volatile int *>(counter) < last - first) {
-              if (++spins > kSpinLimit * 32) { atomicExch(error, 3); break; }
+              if (++spins > kSpinLimit * 32) { atomicExch(q.error, 3); break; }
               __nanosleep(64);
             }
-            *counter = 0;                      // ready for the next launch
+            *counter = 0;                      // ready for the next matmul
           }
-          named_barrier(1, C::CW * 32);
-          if (ck == 0) {
+          named_barrier(1, kCW * 32);
+          if (mine) {
             __threadfence();
             // this CTA's own sums first, then the others' in CTA order: the result does not depend on timing
-            constexpr int BATCH = C::ACC <= 16 ? 4 : C::ACC <= 32 ? 2 : 1;   // contributors whose loads are in flight together
+            constexpr int BATCH = ACC <= 16 ? 4 : 2;   // contributors whose loads are in flight together
             for (int c0 = first; c0 < last; c0 += BATCH) {
-              float4 v[BATCH][C::ACC / 4];
+              float4 v[BATCH][ACC / 4];
 #pragma unroll
               for (int j = 0; j < BATCH; j++) {
-                const float4 *slot = reinterpret_cast<const float4 *>(partials + (size_t)(c0 + j) * C::SLOT) + (size_t)cc * (C::ACC / 4) * 32;
+                const float4 *slot = reinterpret_cast<const float4 *>(q.partials + (size_t)(c0 + j) * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
 #pragma unroll
-                for (int i = 0; i < C::ACC / 4; i++) v[j][i] = c0 + j < last ? __ldcg(slot + i * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < ACC / 4; i++) v[j][i] = c0 + j < last ? __ldcg(slot + i * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
 #pragma unroll
               for (int j = 0; j < BATCH; j++) {
 #pragma unroll
-                for (int i = 0; i < C::ACC / 4; i++)
-                  ACC_AT(4 * i) += v[j][i].x, ACC_AT(4 * i + 1) += v[j][i].y, ACC_AT(4 * i + 2) += v[j][i].z, ACC_AT(4 * i + 3) += v[j][i].w;
+                for (int i = 0; i < ACC / 4; i++)
+                  ACC_OF(acc, 4 * i) += v[j][i].x, ACC_OF(acc, 4 * i + 1) += v[j][i].y, ACC_OF(acc, 4 * i + 2) += v[j][i].z, ACC_OF(acc, 4 * i + 3) += v[j][i].w;
               }
             }
           }
         }
       }
-
-      BT_TRACE(7, threadIdx.x == 0 && q == seg.n - 1 && left == 0);
-      if (finish && ck == 0 && col < p.TC) finish_column<NW, TG>(p, acc, col, cc, lane, arg_v, arg_i);
-      if (p.epi == BT_EPI_ARGMAX && finish) {
-        // the sub-panel's best per token, then, in the last sub-panel to finish, the best over all sub-panels in order
-        named_barrier(1, C::CW * 32);
-        float *part_v = p.part_val;
-        int *part_i = p.part_idx;
-        const int wcols = min(WC, p.TC - done_sp * WC);
-        if (warp == 0) {
-          float v = arg_v[lane];
-          int i = arg_i[lane];
-          for (int c = 1; c < wcols; c++)
-            if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
-          part_v[done_sp * 32 + lane] = v, part_i[done_sp * 32 + lane] = i;
-          __threadfence();
-        }
-        named_barrier(1, C::CW * 32);
-        int *done = p.panels_done;
-        if (threadIdx.x == 0) flags[1] = atomicAdd(done, 1) == subpanels - 1;
-        named_barrier(1, C::CW * 32);
-        if (flags[1]) {
-          __threadfence();
-          if (warp == 0 && lane < p.M) {
-            float v = -INFINITY;
-            int i = 0x7FFFFFFF;
-            for (int qq = 0; qq < subpanels; qq++) {
-              const float ov = __ldcg(part_v + qq * 32 + lane);
-              const int oi = __ldcg(part_i + qq * 32 + lane);
-              if (beats(ov, oi, v, i)) v = ov, i = oi;
+      BT_TRACE(7, threadIdx.x == 0 && last_stage);
+      if (finish) {
+        if (PAIR) {
+          // the up warp hands its sums to the gate warp of the same column
+          float up[2][TG][4];
+#pragma unroll
+          for (int r = 0; r < TG; r++) {        // eight accumulators per lane at a time
+            if (r > 0) named_barrier(1, kCW * 32);
+            if (ck == 1) {
+#pragma unroll
+              for (int i = 0; i < 8; i++) red[(cc * 8 + i) * 32 + lane] = ACC_OF(acc, 8 * r + i);
             }
-            p.arg_val[lane] = v, p.arg_idx[lane] = i + p.arg_base;
+            named_barrier(1, kCW * 32);
+#pragma unroll
+            for (int i = 0; i < 8; i++) ACC_OF(up, 8 * r + i) = red[(cc * 8 + i) * 32 + lane];
           }
-          if (threadIdx.x == 0) *done = 0;
+          if (ck == 0 && col < p.TC) finish_column<TG, true>(p, acc, up, col, cc, lane, arg_v, arg_i);
+        } else if (ck == 0 && col < p.TC) {
+          finish_column<TG, false>(p, acc, acc, col, cc, lane, arg_v, arg_i);
+        }
+        if (!PAIR && p.epi == BT_EPI_ARGMAX) {
+          // the sub-panel's best per token, then, in the last sub-panel to finish, the best over all sub-panels in order
+          named_barrier(1, kCW * 32);
+          const int wcols = min(kWC, p.TC - done_sp * kWC);
+          if (warp == 0) {
+            float v = arg_v[lane];
+            int i = arg_i[lane];
+            for (int c = 1; c < wcols; c++)
+              if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
+            q.part_val[done_sp * 32 + lane] = v, q.part_idx[done_sp * 32 + lane] = i;
+            __threadfence();
+            int is_last = 0;
+            if (lane == 0) is_last = atomicAdd(q.panels_done, 1) == subpanels - 1;
+            is_last = __shfl_sync(0xFFFFFFFFu, is_last, 0);
+            if (is_last) {
+              __threadfence();
+              if (lane < p.M) {
+                float bv = -INFINITY;
+                int bi = 0x7FFFFFFF;
+                for (int s2 = 0; s2 < subpanels; s2++) {
+                  const float ov = __ldcg(q.part_val + s2 * 32 + lane);
+                  const int oi = __ldcg(q.part_idx + s2 * 32 + lane);
+                  if (beats(ov, oi, bv, bi)) bv = ov, bi = oi;
+                }
+                p.arg_val[lane] = bv, p.arg_idx[lane] = bi + p.arg_base;
+              }
+              if (lane == 0) *q.panels_done = 0;
+            }
+          }
         }
       }
-      // the next sub-panel's reduction must not overwrite `red` or the flags while a slower warp still reads them
-      if (C::KS > 1 || p.epi == BT_EPI_ARGMAX) named_barrier(1, C::CW * 32);
+      // the next sub-panel must not overwrite `red` or the argmax staging while a slower warp still reads them
+      named_barrier(1, kCW * 32);
 #pragma unroll
-      for (int i = 0; i < C::ACC; i++) ACC_AT(i) = 0.f;
+      for (int i = 0; i < ACC; i++) ACC_OF(acc, i) = 0.f;
     }
   }
+#undef ACC_OF
   BT_TRACE(4, threadIdx.x == 0);
-#undef ACC_AT
 }
 
-// ---- host side: pick a configuration, size shared memory, launch ----
+__global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid_constant__ Queue q) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int warp = threadIdx.x >> 5, cta = blockIdx.x, ctas = gridDim.x;
+  // The next launch in the stream may start as soon as there is room for its CTAs: what it does before its own
+  // griddepcontrol.wait (set up, prefetch weights) does not depend on this launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBars; s++) {
+      mbar_init(sbase + kSmFull + 8 * s, 1);        // the announcement of the weight bytes
+      mbar_init(sbase + kSmXFull + 8 * s, 1);       // the announcement of the x bytes
+      mbar_init(sbase + kSmEmpty + 8 * s, kCW);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp >= kCW) {
+    if (warp == kCW) produce<true>(q, smem, sbase, cta, ctas);
+    else produce<false>(q, smem, sbase, cta, ctas);
+    return;
+  }
+  Ring ring{0, 0};
+  for (int i = 0; i < q.n; i++) {
+    const GemvParams &p = q.op[i];
+    const int kind = (p.fmt == BT_BFP4 ? 6 : 0) + (p.pair ? 3 : 0) + (p.tg == 1 ? 0 : p.tg == 2 ? 1 : 2);
+    switch (kind) {
+      case 0: consume<BT_BFP8, 1, false>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 1: consume<BT_BFP8, 2, false>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 2: consume<BT_BFP8, 4, false>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 3: consume<BT_BFP8, 1, true>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 4: consume<BT_BFP8, 2, true>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 5: consume<BT_BFP8, 4, true>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 6: consume<BT_BFP4, 1, false>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 7: consume<BT_BFP4, 2, false>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 8: consume<BT_BFP4, 4, false>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 9: consume<BT_BFP4, 1, true>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 10: consume<BT_BFP4, 2, true>(q, p, ring, smem, sbase, cta, ctas); break;
+      default: consume<BT_BFP4, 4, true>(q, p, ring, smem, sbase, cta, ctas); break;
+    }
+    // Report this CTA done with matmul i: its results and partial sums are visible to the whole GPU before the count
+    // moves. A CTA without work in a matmul reports at once, which is harmless: the count of matmul i is complete
+    // only when the CTAs that do have work got their x, that is when matmul i - 1 was complete. The last report of
+    // the last matmul finds every producer past its last look at the counts, and zeroes them for the next launch.
+    // The counts are shared with the launch before this one, which may still be running (this launch may start
+    // early): a CTA without work in the first matmul must not report before that launch is complete.
+    __threadfence();
+    named_barrier(1, kCW * 32);
+    if (threadIdx.x == 0) {
+      if (i == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (atomicAdd(q.ops_done + i, 1) == ctas - 1 && i == q.n - 1)
+        for (int j = 0; j < q.n; j++) q.ops_done[j] = 0;
+    }
+  }
+}
 
-int g_wc[3] = {4, 4, 4};  // tile columns per sub-panel for 1, 2 and 4 token groups
-int g_stages = 0;          // 0: as many as fit
+// ---- host side ---------------------------------------------------------------------------------------------------
+
 unsigned long long *g_trace = nullptr;
+constexpr size_t kTraceStride = 4096;       // timestamps (8 bytes each) between two matmuls' records in a trace buffer
 
-template <int FMT, int NW, int TG, int WC>
-int launch(const GemvParams &base, int sms, cudaStream_t stream) {
-  using C = Config<FMT, NW, TG, WC>;
-  GemvParams p = base;
-  constexpr int kBudget = kSmemBudget / C::OCC - (C::OCC > 1 ? 1024 : 0);     // the runtime keeps 1 KiB per resident CTA
-  int fit = (kBudget - (C::FIXED + 127) / 128 * 128) / C::STAGE;
-  p.nstages = min(kMaxStages, g_stages > 0 ? min(g_stages, fit) : fit);
-  if (p.nstages < 2) return fail(BT_DEVICE, "bt_gemv_bfp: a stage of %d bytes leaves room for %d stages", C::STAGE, p.nstages);
-  const int smem = (C::FIXED + 127) / 128 * 128 + p.nstages * C::STAGE;
-  static bool configured[64] = {};
-  int device = 0;
-  BT_CUDA(cudaGetDevice(&device));
-  if (!configured[device & 63]) {
-    BT_CUDA(cudaFuncSetAttribute(gemv_kernel<FMT, NW, TG, WC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBudget));
-    configured[device & 63] = true;
-  }
-  const long long units = (long long)((p.TC + WC - 1) / WC) * p.KT;
-  const int ctas = (int)min((long long)min(sms * C::OCC, kMaxCtas), units);
-  // x as (8 TG rows x 32 bytes, 2 faces, K tiles): a box picks the rows the MMAs read out of UPS consecutive tiles
-  alignas(64) CUtensorMap xmap;
-  memset(&xmap, 0, sizeof xmap);
-  if (TG < 4) {
-    const uint64_t dims[3] = {(uint64_t)(64 * TG), 2, (uint64_t)p.KT}, strides[2] = {512, 2048};
-    const uint32_t box[3] = {(uint32_t)(64 * TG), 2, (uint32_t)C::UPS};
-    if (int st = make_tmap(&xmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return st;
-  }
-  // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
-  // It only sets up and prefetches weights until its producer warps pass griddepcontrol.wait.
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(C::THREADS), cfg.dynamicSmemBytes = smem, cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
-  BT_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, NW, TG, WC>, p, xmap));
-  return launched("gemv_kernel");
+int check_op(const char *who, int index, const bt_gemv_op &o) {
+  BT_REQUIRE(o.fmt == BT_BFP8 || o.fmt == BT_BFP4, "%s: matmul %d: weights must be bfp8 (8) or bfp4 (4), not %d", who, index, o.fmt);
+  BT_REQUIRE(o.epilogue >= BT_EPI_NONE && o.epilogue <= BT_EPI_ARGMAX, "%s: matmul %d: unknown epilogue %d", who, index, o.epilogue);
+  BT_REQUIRE(o.M >= 1 && o.M <= 32, "%s: matmul %d: takes 1 to 32 rows of x, not %d", who, index, o.M);
+  BT_REQUIRE(o.K > 0 && o.N > 0 && o.K % 32 == 0 && o.N % 32 == 0, "%s: matmul %d: K and N must be positive multiples of 32: %d x %d", who, index, o.K, o.N);
+  BT_REQUIRE((o.N / 32 + kWC - 1) / kWC <= kMaxSubPanels, "%s: matmul %d: N = %d is past the %d columns one matmul handles", who, index, o.N,
+             kMaxSubPanels * kWC * 32);
+  BT_REQUIRE(o.x && o.w && o.x % 16 == 0 && o.w % 16 == 0, "%s: matmul %d: x and w must be 16-byte aligned device addresses", who, index);
+  BT_REQUIRE((o.epilogue == BT_EPI_GLU) == (o.w2 != 0) && o.w2 % 16 == 0, "%s: matmul %d: w2 goes with the GLU epilogue, and only with it", who, index);
+  BT_REQUIRE(o.add % 4 == 0, "%s: matmul %d: the addend must be 4-byte aligned", who, index);
+  if (o.epilogue == BT_EPI_ARGMAX) BT_REQUIRE(o.arg_val && o.arg_idx, "%s: matmul %d: the argmax epilogue needs arg_val and arg_idx", who, index);
+  else BT_REQUIRE(o.out && o.out % 8 == 0 && (o.out_dtype == BT_BF16 || o.out_dtype == BT_FP32), "%s: matmul %d: needs an 8-byte aligned bf16 or fp32 result", who, index);
+  return BT_OK;
 }
 
-template <int FMT, int NW, int TG>
-int launch_wc(const GemvParams &p, int wc, int sms, cudaStream_t stream) {
-  if constexpr (NW == 2 && TG == 4) {
-    return launch<FMT, NW, TG, 12>(p, sms, stream);   // the widest accumulators: see Config::CW
-  } else {
-    if (wc == 8) return launch<FMT, NW, TG, 8>(p, sms, stream);
-    return launch<FMT, NW, TG, 4>(p, sms, stream);
+// Argument checks and the launches shared by the entry points. `scratch` carries the scratch pointers.
+int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Queue &scratch, uint64_t stream) {
+  BT_REQUIRE(n >= 1 && ops, "%s: needs at least one matmul", who);
+  for (int i = 0; i < n; i++)
+    if (int s = check_op(who, i, ops[i])) return s;
+  if (int s = use_device(device)) return s;
+  int sms = 0;
+  BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  // The CTAs of a launch wait for one another, so all of them must fit on the GPU at once.
+  static int resident[64] = {};
+  if (!resident[device & 63]) {
+    BT_CUDA(cudaFuncSetAttribute(gemv_queue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    int per_sm = 0;
+    BT_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_queue_kernel, kThreads, kSmemBytes));
+    if (per_sm < 1) return fail(BT_DEVICE, "%s: the matmul kernel does not fit an SM of device %d", who, device);
+    resident[device & 63] = min(per_sm, kOcc);
   }
+  const int ctas = min(sms * resident[device & 63], kMaxCtas);
+  for (int base = 0; base < n; base += kQueueMax) {
+    Queue q = scratch;
+    q.n = min(kQueueMax, n - base);
+    for (int i = 0; i < q.n; i++) {
+      const bt_gemv_op &o = ops[base + i];
+      GemvParams &p = q.op[i];
+      p.x = as_ptr<uint8_t>(o.x), p.w[0] = as_ptr<uint8_t>(o.w), p.w[1] = as_ptr<uint8_t>(o.w2), p.add = as_ptr<uint16_t>(o.add);
+      p.out = as_ptr<void>(o.out), p.arg_val = as_ptr<float>(o.arg_val), p.arg_idx = as_ptr<int>(o.arg_idx);
+      p.trace = g_trace ? g_trace + (size_t)(base + i) * kTraceStride : nullptr;
+      p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32;
+      p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
+    }
+    // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
+    // It only sets up and prefetches weights until its producer threads pass griddepcontrol.wait.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = kSmemBytes, cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    BT_CUDA(cudaLaunchKernelEx(&cfg, gemv_queue_kernel, q));
+    if (int st = launched("gemv_queue_kernel")) return st;
+  }
+  return BT_OK;
 }
 
-template <int FMT, int NW>
-int launch_tg(const GemvParams &p, int wc_force, int sms, cudaStream_t stream) {
-  if (p.M <= 8) return launch_wc<FMT, NW, 1>(p, wc_force ? wc_force : g_wc[0], sms, stream);
-  if (p.M <= 16) return launch_wc<FMT, NW, 2>(p, wc_force ? wc_force : g_wc[1], sms, stream);
-  return launch_wc<FMT, NW, 4>(p, wc_force ? wc_force : g_wc[2], sms, stream);
+Queue workspace_scratch(uint64_t work) {
+  Queue q{};
+  q.error = as_ptr<int>(work + kWsError), q.panels_done = as_ptr<int>(work + kWsPanelsDone), q.ops_done = as_ptr<int>(work + kWsOpsDone);
+  q.counters = as_ptr<int>(work + kWsCounters), q.part_val = as_ptr<float>(work + kWsArgVal), q.part_idx = as_ptr<int>(work + kWsArgIdx);
+  q.partials = as_ptr<float>(work + kWsPartials), q.slot_floats = (int)kSlotFloatsMax;
+  return q;
 }
 
 }  // namespace
@@ -578,13 +740,13 @@ int launch_tg(const GemvParams &p, int wc_force, int sms, cudaStream_t stream) {
 // at reduced limits: up to 8 rows of x, up to kStaticSubPanels sub-panels of 4 tile columns.
 namespace {
 constexpr int kStaticSubPanels = 4096;                                  // N <= 4096 * 4 * 32 = 524288 columns
-constexpr size_t kStaticSlotFloats = 4 * 16 * 32;                       // WC = 4, up to 16 accumulators per lane
+constexpr size_t kStaticSlotFloats = 8 * 8 * 32;                        // 8 warps, 8 accumulators per lane
 constexpr size_t kStCounters = 256;
 constexpr size_t kStControlBytes = kStCounters + 4 * (size_t)kStaticSubPanels;   // what must be zero when a call starts
 constexpr size_t kStArgVal = kStControlBytes;
 constexpr size_t kStArgIdx = kStArgVal + 4 * 32 * (size_t)kStaticSubPanels;
 constexpr size_t kStPartials = kStArgIdx + 4 * 32 * (size_t)kStaticSubPanels;
-constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 3.1 MB
+constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 3.7 MB
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
@@ -597,55 +759,17 @@ int bt_gemv_workspace_bytes(int device, size_t *bytes) {
   return BT_OK;
 }
 
-// Tuning knobs for experiments: tile columns per sub-panel (4, 8 or 16) for up to 8, 16 and 32 token rows, and the
-// number of pipeline stages (0 = as many as fit). Values of 0 keep the current setting.
-int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages) {
-  const int wc[3] = {wc_m8, wc_m16, wc_m32};
-  for (int i = 0; i < 3; i++) {
-    BT_REQUIRE(wc[i] == 0 || wc[i] == 4 || wc[i] == 8, "bt_gemv_tune: sub-panel width must be 4 or 8, not %d", wc[i]);
-    if (wc[i]) g_wc[i] = wc[i];
-  }
-  BT_REQUIRE(stages >= 0 && stages <= kMaxStages, "bt_gemv_tune: stages must be 0..%d", kMaxStages);
-  g_stages = stages;
-  return BT_OK;
-}
-
-// Argument checks and the launch shared by the entry points. `scratch` carries the scratch pointers; wc_force, when
-// nonzero, fixes the sub-panel width.
-static int gemv_common(const char *who, int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
-                       uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base,
-                       const GemvParams &scratch, int wc_force, uint64_t stream) {
-  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "%s: weights must be bfp8 (8) or bfp4 (4), not %d", who, fmt);
-  BT_REQUIRE(epilogue >= BT_EPI_NONE && epilogue <= BT_EPI_ARGMAX, "%s: unknown epilogue %d", who, epilogue);
-  BT_REQUIRE(M >= 1 && M <= 32, "%s: takes 1 to 32 rows of x, not %d", who, M);
-  BT_REQUIRE(K > 0 && N > 0 && K % 32 == 0 && N % 32 == 0, "%s: K and N must be positive multiples of 32: %d x %d", who, K, N);
-  BT_REQUIRE(x && w && x % 16 == 0 && w % 16 == 0, "%s: x and w must be 16-byte aligned device addresses", who);
-  BT_REQUIRE((epilogue == BT_EPI_GLU) == (w2 != 0) && w2 % 16 == 0, "%s: w2 goes with the GLU epilogue, and only with it", who);
-  BT_REQUIRE(add % 4 == 0, "%s: the addend must be 4-byte aligned", who);
-  if (epilogue == BT_EPI_ARGMAX) BT_REQUIRE(arg_val && arg_idx, "%s: the argmax epilogue needs arg_val and arg_idx", who);
-  else BT_REQUIRE(out && out % 8 == 0 && (out_dtype == BT_BF16 || out_dtype == BT_FP32), "%s: needs an 8-byte aligned bf16 or fp32 result", who);
-  if (int s = use_device(device)) return s;
-  int sms = 0;
-  BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  GemvParams p = scratch;
-  p.x = as_ptr<uint8_t>(x), p.w[0] = as_ptr<uint8_t>(w), p.w[1] = as_ptr<uint8_t>(w2), p.add = as_ptr<uint16_t>(add);
-  p.out = as_ptr<void>(out), p.arg_val = as_ptr<float>(arg_val), p.arg_idx = as_ptr<int>(arg_idx);
-  p.trace = g_trace;
-  p.alpha = alpha, p.arg_base = arg_base, p.M = M, p.KT = K / 32, p.TC = N / 32, p.epi = epilogue, p.out_fp32 = out_dtype == BT_FP32;
-  cudaStream_t st = as_stream(stream);
-  if (fmt == BT_BFP8) return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP8, 2>(p, wc_force, sms, st) : launch_tg<BT_BFP8, 1>(p, wc_force, sms, st);
-  return epilogue == BT_EPI_GLU ? launch_tg<BT_BFP4, 2>(p, wc_force, sms, st) : launch_tg<BT_BFP4, 1>(p, wc_force, sms, st);
+int bt_gemv_queue(int device, int n, const bt_gemv_op *ops, uint64_t work, size_t work_bytes, uint64_t stream) {
+  BT_REQUIRE(work && work % 16 == 0 && work_bytes >= kWsBytes, "bt_gemv_queue: needs %zu bytes of 16-byte aligned scratch, got %zu", kWsBytes, work_bytes);
+  return enqueue("bt_gemv_queue", device, n, ops, workspace_scratch(work), stream);
 }
 
 int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2, uint64_t add,
                 float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx, int arg_base, uint64_t work,
                 size_t work_bytes, uint64_t stream) {
   BT_REQUIRE(work && work % 16 == 0 && work_bytes >= kWsBytes, "bt_gemv_bfp: needs %zu bytes of 16-byte aligned scratch, got %zu", kWsBytes, work_bytes);
-  BT_REQUIRE(N <= 0 || (N / 32 + 3) / 4 <= kMaxSubPanels, "bt_gemv_bfp: N = %d is past the %d columns one launch handles", N, kMaxSubPanels * 128);
-  GemvParams scratch{};
-  scratch.error = as_ptr<int>(work + kWsError), scratch.panels_done = as_ptr<int>(work + kWsPanelsDone), scratch.counters = as_ptr<int>(work + kWsCounters);
-  scratch.part_val = as_ptr<float>(work + kWsArgVal), scratch.part_idx = as_ptr<int>(work + kWsArgIdx), scratch.partials = as_ptr<float>(work + kWsPartials);
-  return gemv_common("bt_gemv_bfp", device, fmt, epilogue, M, K, N, x, w, w2, add, alpha, out, out_dtype, arg_val, arg_idx, arg_base, scratch, 0, stream);
+  const bt_gemv_op op = {fmt, epilogue, M, K, N, out_dtype, arg_base, alpha, x, w, w2, add, out, arg_val, arg_idx};
+  return enqueue("bt_gemv_bfp", device, 1, &op, workspace_scratch(work), stream);
 }
 
 // The device address of g_static_scratch on `device`, looked up once per device. In host code the array's name is
@@ -670,22 +794,24 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   BT_REQUIRE(M <= 8, "bt_gemv_bfp_static: the built-in scratch holds up to 8 rows of x, not %d; use bt_gemv_bfp with your own scratch", M);
   BT_REQUIRE(N <= kStaticSubPanels * 128, "bt_gemv_bfp_static: the built-in scratch holds up to %d columns, not %d; use bt_gemv_bfp with your own scratch",
              kStaticSubPanels * 128, N);
+  const bt_gemv_op op = {fmt, epilogue, M, K, N, out_dtype, arg_base, alpha, x, w, w2, add, out, arg_val, arg_idx};
+  if (int s = check_op("bt_gemv_bfp_static", 0, op)) return s;
   unsigned char *base = nullptr;
   if (int s = static_scratch(device, &base)) return s;
   if (int s = use_device(device)) return s;
   // the array keeps whatever the last call left: flags and arrival counters must start at zero
   BT_CUDA(cudaMemsetAsync(base, 0, kStControlBytes, as_stream(stream)));
-  GemvParams scratch{};
-  scratch.error = reinterpret_cast<int *>(base), scratch.panels_done = reinterpret_cast<int *>(base + 4);
-  scratch.counters = reinterpret_cast<int *>(base + kStCounters);
+  Queue scratch{};
+  scratch.error = reinterpret_cast<int *>(base + kWsError), scratch.panels_done = reinterpret_cast<int *>(base + kWsPanelsDone);
+  scratch.ops_done = reinterpret_cast<int *>(base + kWsOpsDone), scratch.counters = reinterpret_cast<int *>(base + kStCounters);
   scratch.part_val = reinterpret_cast<float *>(base + kStArgVal), scratch.part_idx = reinterpret_cast<int *>(base + kStArgIdx);
-  scratch.partials = reinterpret_cast<float *>(base + kStPartials);
-  return gemv_common("bt_gemv_bfp_static", device, fmt, epilogue, M, K, N, x, w, w2, add, alpha, out, out_dtype, arg_val, arg_idx, arg_base, scratch,
-                     4, stream);
+  scratch.partials = reinterpret_cast<float *>(base + kStPartials), scratch.slot_floats = (int)kStaticSlotFloats;
+  return enqueue("bt_gemv_bfp_static", device, 1, &op, scratch, stream);
 }
 
-// Debugging aid: when `buffer` is nonzero, every later launch writes 8 nanosecond timestamps per CTA into it (kernel
-// start, barriers ready, first stage arrived, last stage consumed, kernel end, last copy issued). 0 turns it off.
+// Debugging aid: when `buffer` is nonzero, every later matmul writes 8 nanosecond timestamps per CTA into it
+// (start, -, first stage arrived, last stage consumed, end, last copy issued, k halves added, partial sums
+// combined); matmul i of a queue writes at buffer + i * 32 KiB. 0 turns it off. Only the trace build records.
 int bt_gemv_trace(uint64_t buffer) {
   g_trace = as_ptr<unsigned long long>(buffer);
   return BT_OK;

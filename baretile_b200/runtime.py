@@ -34,7 +34,8 @@ def _merge_holes(holes):
 class Recording:
   """Launches recorded once and replayed with one call: the reference's Recording / tensor.jit
   (baretile/tensor.py:1171-1293), which replays a block of commands with one doorbell write. Here the block is a
-  CUDA graph. Recorded launches keep their addresses, so the tensors they use must stay alive.
+  CUDA graph, and matmuls that follow one another in it become one queue launch (see Runtime.queue). Recorded
+  launches keep their addresses, so the tensors they use must stay alive.
 
       with rt.record() as step: y = (x @ w).relu().realize()
       step.replay()
@@ -42,12 +43,19 @@ class Recording:
   def __init__(self, rt): self.rt, self.graph, self.count = rt, None, 0
   def __enter__(self):
     self.rt.check()
+    self.rt.flush()
     self.first = self.rt.launches
     _lib.call("bt_graph_begin", self.rt.device, self.rt.stream)
+    self.outer, self.rt.pending = self.rt.pending, []
     return self
   def __exit__(self, kind, *_):
     graph = ctypes.c_uint64()
-    try: _lib.call("bt_graph_end", self.rt.device, self.rt.stream, ctypes.byref(graph))
+    try:
+      try:
+        if kind is None: self.rt.flush()
+      finally:
+        self.rt.pending = self.outer
+        _lib.call("bt_graph_end", self.rt.device, self.rt.stream, ctypes.byref(graph))
     except Exception:
       if kind is None: raise
       return
@@ -60,6 +68,25 @@ class Recording:
   def close(self):
     if self.graph is not None and self.rt.active: _lib.lib().bt_graph_destroy(self.rt.device, self.graph)
     self.graph = None
+
+
+class Queue:
+  """Inside `with rt.queue():` matmuls of up to 32 rows are collected instead of launched, and go out together as
+  one bt_gemv_queue launch when the block ends or when anything else needs the stream (another kind of launch, a
+  copy, wait). The kernel runs them in order and keeps streaming weights across the boundaries between them, which
+  is what a chain of dependent decode matmuls needs. The reference queues commands in a ring that its dispatcher
+  drains without the host (baretile/runtime.py:734-771); this is the same idea for the path's matmuls."""
+  def __init__(self, rt): self.rt = rt
+  def __enter__(self):
+    self.rt.check()
+    self.outer = self.rt.pending
+    if self.outer is None: self.rt.pending = []
+    return self
+  def __exit__(self, kind, *_):
+    try:
+      if kind is None: self.rt.flush()
+    finally:
+      if self.outer is None: self.rt.pending = None
 
 
 class Runtime:
@@ -77,6 +104,7 @@ class Runtime:
     self.sent = {}                                   # launch number % TIMES -> (name, start event, end event)
     self.numbers = {}                                # 1 x 1 tensors of Python numbers, made once
     self.log = None
+    self.pending = None      # matmuls collected for one queue launch (a list while queueing)
     self.stream = ctypes.c_uint64()
     for other in list(chip.taken.values()): other.close()
     _lib.call("bt_stream_create", self.device, ctypes.byref(self.stream))
@@ -132,6 +160,11 @@ class Runtime:
     self.check()
     if units is not None and not 1 <= int(units) < 2**32: raise ValueError("launch units must be in [1, 2**32 - 1]")
     if self.log is not None: self.log.append((kernel, args, units, name))
+    if self.pending is not None and kernel == "bt_gemv_bfp":
+      self.pending.append(args)
+      self._count(name or kernel, 0, 0)
+      return
+    self.flush()
     start = end = 0
     if self.timing:
       start, end = ctypes.c_uint64(), ctypes.c_uint64()
@@ -141,12 +174,27 @@ class Runtime:
       _lib.call("bt_event_record", self.device, start, self.stream)
     _lib.call(kernel, self.device, *args, self.stream)
     if self.timing: _lib.call("bt_event_record", self.device, end, self.stream)
+    self._count(name or kernel, start, end)
+
+  def _count(self, name, start, end):
     self.launches += 1
     old = self.sent.pop(self.launches % TIMES, None)
     if old:
       for e in old[1:]:
         if e: _lib.lib().bt_event_destroy(self.device, e)
-    self.sent[self.launches % TIMES] = (name or kernel, start, end)
+    self.sent[self.launches % TIMES] = (name, start, end)
+
+  def queue(self): return Queue(self)
+
+  def flush(self):
+    """Send the matmuls collected so far as one queue launch."""
+    if not self.pending: return
+    ops, self.pending = self.pending, []
+    arr = (_lib.GemvOp * len(ops))()
+    for o, (fmt, epi, m, k, n, x, w, w2, add, alpha, out, out_dtype, arg_val, arg_idx, arg_base, _work, _bytes) in zip(arr, ops):
+      o.fmt, o.epilogue, o.M, o.K, o.N, o.out_dtype, o.arg_base, o.alpha = fmt, epi, m, k, n, out_dtype, arg_base, getattr(alpha, "value", alpha)
+      o.x, o.w, o.w2, o.add, o.out, o.arg_val, o.arg_idx = x, w, w2, add, out, arg_val, arg_idx
+    _lib.call("bt_gemv_queue", self.device, len(ops), arr, self.work, self.work_bytes, self.stream)
 
   def wait(self, timeout=60, launch=None):
     """Block until the queued launches are done (baretile/runtime.py:858-880). On timeout raise TimeoutError; the
@@ -154,6 +202,7 @@ class Runtime:
     self.check()
     if launch is not None and launch > self.launches:
       raise ValueError(f"launch {launch} was never queued; the last one queued is {self.launches}")
+    self.flush()
     _lib.call("bt_stream_sync", self.device, self.stream, int(timeout * 1000))
     error = ctypes.c_int()
     _lib.call("bt_gemv_check", self.device, self.work, self.stream, ctypes.byref(error))
@@ -223,11 +272,13 @@ class Runtime:
   def upload_async(self, addr, buf, n=None):
     """Queue a copy from page-locked host memory to device memory; returns at once."""
     self.check()
+    self.flush()
     _lib.call("bt_h2d", self.device, addr, ctypes.addressof(buf), len(buf) if n is None else n, self.stream)
 
   def download_async(self, buf, addr, n=None):
     """Queue a copy from device memory into page-locked host memory; wait() before reading it."""
     self.check()
+    self.flush()
     _lib.call("bt_d2h", self.device, ctypes.addressof(buf), addr, len(buf) if n is None else n, self.stream)
 
   def upload(self, addr, data):
@@ -235,6 +286,7 @@ class Runtime:
     self.check()
     data = bytes(data) if not isinstance(data, (bytes, bytearray)) else data
     buf = (ctypes.c_char * len(data)).from_buffer_copy(data)
+    self.flush()
     _lib.call("bt_h2d", self.device, addr, ctypes.cast(buf, ctypes.c_void_p), len(data), self.stream)
     _lib.call("bt_stream_sync", self.device, self.stream, -1)   # buf is pageable and short-lived
 
@@ -242,6 +294,7 @@ class Runtime:
     """n bytes of device memory at addr, after the queued launches."""
     self.check()
     buf = ctypes.create_string_buffer(n)
+    self.flush()
     _lib.call("bt_d2h", self.device, ctypes.cast(buf, ctypes.c_void_p), addr, n, self.stream)
     _lib.call("bt_stream_sync", self.device, self.stream, -1)
     return buf.raw

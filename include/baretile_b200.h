@@ -113,6 +113,19 @@ int bt_gemv_workspace_bytes(int device, size_t *bytes);
 int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
                 uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx,
                 int arg_base, uint64_t work, size_t work_bytes, uint64_t stream);
+/* ---- a queue of matmuls in one launch: the command ring the dispatcher drains (baretile/runtime.py:734-771,
+ * the resident dispatcher :369-446) ----
+ * Runs ops[0..n) in order, each exactly as bt_gemv_bfp would, as one kernel (one per 32 matmuls): a matmul may read
+ * what any earlier one wrote (its x, its addend), as in a decode step where each result feeds the next. Between two
+ * matmuls the GPU keeps streaming: the weights of the next one are fetched while the previous one finishes, and only
+ * its x waits. The weights (w, w2) must not be written by an earlier matmul of the same call or by the launch right
+ * before it in the stream. The fields of bt_gemv_op are bt_gemv_bfp's arguments of the same names. */
+typedef struct bt_gemv_op {
+  int fmt, epilogue, M, K, N, out_dtype, arg_base;
+  float alpha;
+  uint64_t x, w, w2, add, out, arg_val, arg_idx;
+} bt_gemv_op;
+int bt_gemv_queue(int device, int n, const bt_gemv_op *ops, uint64_t work, size_t work_bytes, uint64_t stream);
 /* ---- the matmul: fused_kernel's prefill grid (baretile/kernels.py:205-215, :470-506, grid_parts :18-39) ----
  * out[M, N] = epilogue(alpha * (a[M, K] @ W[K, N])) for many rows, on the tcgen05 tensor cores with fp32
  * accumulators in tensor memory. The weights are expanded from block float to exact bf16 inside the kernel.
@@ -128,7 +141,7 @@ int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
  * Some embedders of this library run where cudaMalloc is off limits -- inside another framework's capture or
  * allocator-owned region, in a process whose memory budget was handed out in full at start-up, or in a plug-in
  * that is only ever given its input and output buffers. For them the scratch that bt_gemv_bfp takes from the
- * caller sits in a fixed array inside the library's device image (about 3.1 MB on every GPU that loads the
+ * caller sits in a fixed array inside the library's device image (about 3.7 MB on every GPU that loads the
  * library, held until the process exits). The call allocates and frees nothing, on the host side either.
  * Limits, rejected with BT_BAD_ARGUMENT: M <= 8 rows of x, N <= 524288 columns. Inputs and outputs are the
  * caller's, exactly as for bt_gemv_bfp. The first call on a device looks the array's address up (one runtime
@@ -142,13 +155,9 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
  * unreliable): the counterpart of Runtime.wait's timeout report (baretile/runtime.py:866-876). Synchronises the
  * stream, and clears the flag. */
 int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error);
-/* Tuning knobs (the reference's module constants tensix.DEPTH / CHUNKS, baretile/tensix.py:716-722): tile columns
- * per sub-panel (4, 8 or 16) for up to 8, 16 and 32 rows of x, and pipeline stages (0: as many as fit). A 0 for a
- * width keeps the current setting. */
-int bt_gemv_tune(int wc_m8, int wc_m16, int wc_m32, int stages);
-/* Debugging aid (the reference's kernel print rings, baretile/runtime.py:882-901): with a nonzero device buffer of
- * 32 KiB, every later matmul launch writes 8 nanosecond timestamps per CTA into it, and CTA 0 adds four cycle
- * counts for each of its first 64 stages. 0 turns it off. */
+/* Debugging aid (the reference's kernel print rings, baretile/runtime.py:882-901): with a nonzero device buffer,
+ * every later matmul writes 8 nanosecond timestamps per CTA into it, matmul i of a queue at buffer + i * 32 KiB.
+ * 0 turns it off. Only a library built with -DBT_GEMV_TRACE records anything. */
 int bt_gemv_trace(uint64_t buffer);
 /* Number of GPU kernels this library has launched on behalf of the calling process. */
 int bt_launch_count(uint64_t *count);

@@ -47,8 +47,10 @@ def test_argument_checks_need_no_device(built):
   with pytest.raises(ValueError, match="1 to 32 rows"): _lib.call("bt_gemv_bfp", 0, 8, 0, 40, 64, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, 256, 1 << 30, 0)
   with pytest.raises(ValueError, match="multiples of 32"): _lib.call("bt_gemv_bfp", 0, 8, 0, 8, 60, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, 256, 1 << 30, 0)
   with pytest.raises(ValueError, match="GLU"): _lib.call("bt_gemv_bfp", 0, 8, 3, 8, 64, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, 256, 1 << 30, 0)
-  with pytest.raises(ValueError, match="sub-panel width"): _lib.call("bt_gemv_tune", 5, 0, 0, 0)
-  assert b"sub-panel" in _lib.lib().bt_last_error()
+  op = _lib.GemvOp(fmt=8, epilogue=0, M=8, K=64, N=60, out_dtype=0, alpha=1.0, x=256, w=256, out=256)
+  with pytest.raises(ValueError, match="matmul 0: K and N"): _lib.call("bt_gemv_queue", 0, 1, ctypes.byref(op), 256, 1 << 30, 0)
+  with pytest.raises(ValueError, match="at least one"): _lib.call("bt_gemv_queue", 0, 0, ctypes.byref(op), 256, 1 << 30, 0)
+  assert b"at least one" in _lib.lib().bt_last_error()
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -123,21 +123,80 @@ def test_llama_shapes(rt, fmt, k, n):
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
 def test_every_configuration(rt, fmt):
-  # each sub-panel width (4 or 8 tile columns) and a short pipeline, for each group of row counts
-  from baretile_b200 import _lib
+  # each group of row counts, one matrix and the gate/up pair, on shapes with ragged sub-panels and short ranges
   rng = np.random.default_rng(13)
   w, w2 = weights(rng, 2048, 1184), weights(rng, 2048, 1184)
-  try:
-    for wc in (4, 8):
-      for stages in (2, 0):
-        _lib.call("bt_gemv_tune", wc, wc, wc, stages)
-        for m in (2, 16, 32):
-          x = acts(rng, m, 2048)
-          got, ref = run(rt, x, w, fmt, "glu", w2)
-          check_matmul(got, x, None, ref, TOL_BF16)
-          got, ref = run(rt, x, w, fmt, dtype="fp32")
-          check_matmul(got, x, None, ref, TOL_FP32)
-  finally: _lib.call("bt_gemv_tune", 4, 4, 4, 0)
+  for m in (2, 16, 32):
+    x = acts(rng, m, 2048)
+    got, ref = run(rt, x, w, fmt, "glu", w2)
+    check_matmul(got, x, None, ref, TOL_BF16)
+    got, ref = run(rt, x, w, fmt, dtype="fp32")
+    check_matmul(got, x, None, ref, TOL_FP32)
+
+
+def _layer_chain(rt, x, layers):
+  """x through a chain of dependent matmuls: each layer is (gate, up, down) Tensors; returns every layer's output."""
+  outs, h = [], x
+  for wg, wu, wd in layers:
+    a = ((h @ wg).silu() * (h @ wu)).realize()
+    h = (a @ wd).relu().realize()
+    outs += [a, h]
+  return outs
+
+
+@pytest.mark.parametrize("m", [1, 8, 20])
+def test_queue_equals_separate_launches(rt, m):
+  # a chain where every matmul reads the one before it, mixed formats: one queue launch gives the same bits as one
+  # launch per matmul, and matches the oracle
+  rng = np.random.default_rng(31 + m)
+  shapes = [(512, 1536, "bfp8"), (512, 736, "bfp4"), (512, 1536, "bfp4"), (512, 2048, "bfp8")]
+  host = [(weights(rng, k, n) * 2, weights(rng, k, n) * 2, weights(rng, n, 512) * 2, fmt) for k, n, fmt in shapes]
+  layers = [tuple(upload(rt, w).cast(fmt).columns() for w in (wg, wu, wd)) for wg, wu, wd, fmt in host]
+  x = acts(rng, m, 512)
+  tx = upload(rt, x)
+  separate = [t.numpy() for t in _layer_chain(rt, tx, layers)]
+  rt.log = []
+  with rt.queue(): queued = _layer_chain(rt, tx, layers)
+  rt.wait()
+  log, rt.log = rt.log, None
+  assert len(log) == 2 * len(layers) and all(kernel == "bt_gemv_bfp" for kernel, *_ in log)
+  for got, want in zip(queued, separate): assert np.array_equal(got.numpy(), want)
+  h = x
+  for (wg, wu, wd, fmt), a, out in zip(host, separate[0::2], separate[1::2]):
+    ref = o.silu(h @ o.dequant(wg, fmt)) * (h @ o.dequant(wu, fmt))
+    check_matmul(a, h, None, ref, TOL_BF16)
+    check_matmul(out, a, None, np.maximum(a @ o.dequant(wd, fmt), 0), TOL_BF16)
+    h = out
+
+
+def test_queue_longer_than_one_launch(rt):
+  # 40 dependent matmuls: more than one kernel's worth (32), so the list is cut and the second kernel waits for the first
+  rng = np.random.default_rng(5)
+  w = upload(rt, bf16(np.eye(256, dtype=np.float32) * 1.0)).cast("bfp8").columns()
+  x = acts(rng, 4, 256)
+  h = upload(rt, x)
+  from baretile_b200 import _lib
+  before, count = ctypes.c_uint64(), ctypes.c_uint64()
+  _lib.call("bt_launch_count", ctypes.byref(before))
+  with rt.queue():
+    for _ in range(40): h = (h @ w).realize()
+  rt.wait()
+  _lib.call("bt_launch_count", ctypes.byref(count))
+  assert count.value - before.value == 2
+  assert np.array_equal(h.numpy(), x)                               # x @ I, forty times
+
+
+def test_queue_is_flushed_by_a_read(rt):
+  # reading a result back inside the block sends what was collected first
+  rng = np.random.default_rng(6)
+  x, w = acts(rng, 2, 256), weights(rng, 256, 256)
+  tx, tw = upload(rt, x), upload(rt, w).cast("bfp8").columns()
+  with rt.queue():
+    y = (tx @ tw).realize()
+    got = y.numpy()
+    z = (y @ tw).realize()
+  check_matmul(got, x, None, x @ o.dequant(w, "bfp8"), TOL_BF16)
+  check_matmul(z.numpy(), got, None, got @ o.dequant(w, "bfp8"), TOL_BF16)
 
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
