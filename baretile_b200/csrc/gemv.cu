@@ -50,8 +50,8 @@ constexpr int kQueueMax = 32;               // matmuls per launch; longer lists 
 constexpr uint32_t kSpinLimit = 1u << 14;   // attempts of up to 100 us each (mbarriers) or 32-64 ns polls x 32 (counters)
 
 // Shared memory of a CTA.
-constexpr int kSmFull = 0, kSmXFull = 128, kSmEmpty = 256;  // mbarriers: a stage's weights landed, its x landed, it is free again
-constexpr int kSmHeld = 384;                // uint32[2][kBars]: ring bytes of each stage in the ring, as each producer warp noted them
+constexpr int kSmFull = 0, kSmEmpty = 128;  // mbarriers: a stage's weights and x have landed; it is free again
+constexpr int kSmHeld = 256;                // uint32[2][kBars]: ring bytes of each stage in the ring, as each producer warp noted them
 constexpr int kSmArgVal = 512;              // float[4][32]: best value per column warp and token
 constexpr int kSmArgIdx = 512 + 512;        // int[4][32]: and its channel
 constexpr int kSmRed = 1536;                // 4 KiB: 8 accumulators per lane handed from warps ck = 1 to warps ck = 0
@@ -60,16 +60,19 @@ constexpr int kSmemBytes = (228 * 1024 / kOcc - 1024) / 128 * 128;   // an SM's 
 constexpr int kRingBytes = kSmemBytes - kSmRing;
 static_assert(kSmRing % 128 == 0 && kRingBytes % 128 == 0, "stages are 128-byte aligned");
 
-// Scratch layout (byte offsets into the caller's workspace).
+// Scratch layout (byte offsets into the caller's workspace). Two matmuls of a queue may be in flight at once, so
+// what a matmul uses while it runs exists twice (a set for even and one for odd positions in the queue).
 constexpr size_t kWsError = 0;                                   // int: set to nonzero when a wait gave up
-constexpr size_t kWsPanelsDone = 4;                              // int: sub-panels finished (argmax epilogue)
 constexpr size_t kWsOpsDone = 8;                                 // int[kQueueMax]: CTAs that finished each matmul of the launch
-constexpr size_t kWsCounters = 256;                              // int[kMaxSubPanels]: CTAs arrived at a sub-panel
-constexpr size_t kWsArgVal = kWsCounters + 4 * kMaxSubPanels;    // float[kMaxSubPanels][32]
-constexpr size_t kWsArgIdx = kWsArgVal + 4 * 32 * kMaxSubPanels; // int[kMaxSubPanels][32]
-constexpr size_t kWsPartials = kWsArgIdx + 4 * 32 * kMaxSubPanels;
+constexpr size_t kWsSets = 256;                                  // the sets start here
+constexpr size_t kSetPanelsDone = 0;                             // int: sub-panels finished (argmax epilogue)
+constexpr size_t kSetCounters = 256;                             // int[kMaxSubPanels]: CTAs arrived at a sub-panel
+constexpr size_t kSetArgVal = kSetCounters + 4 * kMaxSubPanels;  // float[kMaxSubPanels][32]
+constexpr size_t kSetArgIdx = kSetArgVal + 4 * 32 * kMaxSubPanels;   // int[kMaxSubPanels][32]
+constexpr size_t kSetPartials = kSetArgIdx + 4 * 32 * kMaxSubPanels;
 constexpr size_t kSlotFloatsMax = 8 * 32 * 32;                   // 8 warps x up to 32 accumulators x 32 lanes
-constexpr size_t kWsBytes = kWsPartials + (size_t)kMaxCtas * kSlotFloatsMax * 4;
+constexpr size_t kSetBytes = kSetPartials + (size_t)kMaxCtas * kSlotFloatsMax * 4;
+constexpr size_t kWsBytes = kWsSets + 2 * kSetBytes;
 
 // The shape of a stage for one kind of matmul: format, one matrix or a gate/up pair, token groups of 8 rows.
 struct Geometry {
@@ -78,17 +81,17 @@ struct Geometry {
   int ups;       // units (tile rows) per stage
   int matrix;    // bytes of one matrix's part of a stage
   int w_bytes;   // all weights of a stage; the x tiles follow
-  int xb;        // bytes of an x tile (staged whole)
+  int xb;        // bytes of an x tile staged: its first half (token rows 0-15) or all of it
   int stage;     // bytes of a stage
 };
-__host__ __device__ constexpr int stage_rows_per_warp(int fmt, int tg) { return tg == 4 ? 1 : 2; }
+__host__ __device__ constexpr int stage_rows_per_warp(int fmt, int tg) { return tg == 1 && fmt == BT_BFP4 ? 4 : 2; }
 __host__ __device__ constexpr Geometry geometry(int fmt, bool pair, int tg) {
   Geometry g{};
   g.tb = tile_bytes(fmt), g.t = stage_rows_per_warp(fmt, tg);
   g.ups = pair ? g.t : 2 * g.t;
   g.matrix = g.ups * kWC * g.tb;
   g.w_bytes = (pair ? 2 : 1) * g.matrix;
-  g.xb = 2048;
+  g.xb = tg == 4 ? 2048 : 1024;
   g.stage = g.w_bytes + g.ups * g.xb;
   return g;
 }
@@ -107,16 +110,24 @@ struct GemvParams {
   float alpha;
   int arg_base, M, KT, TC, epi, out_fp32;
   int fmt, pair, tg;
+  int wait_for;               // the matmul of the launch that must be complete before this one starts; -1: none
 };
 
-// What one launch gets: the matmuls and the scratch they share. The scratch holds a
-// wait-gave-up flag, the counts of finished sub-panels (argmax) and finished matmuls, the arrivals per sub-panel
-// (all zero before first use; the kernel leaves them zero), per-sub-panel argmax candidates and one slot of partial
-// sums per CTA.
+// What a matmul uses while it runs: the count of finished sub-panels (argmax), the arrivals per sub-panel (both
+// zero before first use; the kernel leaves them zero), per-sub-panel argmax candidates and one slot of partial sums
+// per CTA.
+struct Scratch {
+  int *panels_done, *counters, *part_idx;
+  float *part_val, *partials;
+};
+
+// What one launch gets: the matmuls and the scratch they share: a wait-gave-up flag, the counts of CTAs that
+// finished each matmul (zero before first use; the kernel leaves them zero) and one or two sets of running scratch.
 struct Queue {
   int n;
-  int *error, *panels_done, *ops_done, *counters, *part_idx;
-  float *part_val, *partials;
+  int sets;                   // 2: matmuls alternate between the sets, and two may be in flight; 1: one after the other
+  int *error, *ops_done;
+  Scratch set[2];
   int slot_floats;            // floats between two CTAs' slots of partial sums
   GemvParams op[kQueueMax];
 };
@@ -276,6 +287,7 @@ struct Segments {
 __device__ __forceinline__ Segments segments_of(long long u0, long long u1, int KT) {
   Segments s;
   s.n = 0;
+  for (int i = 0; i < 3; i++) s.a[i] = s.b[i] = 0;
   if (u0 >= u1) return s;
   const long long head_end = min(u1, (u0 / KT + 1) * KT);            // end of the sub-panel the range starts in
   const bool head_partial = u0 % KT != 0 || head_end - u0 < KT;
@@ -288,39 +300,44 @@ __device__ __forceinline__ Segments segments_of(long long u0, long long u1, int 
   return s;
 }
 
-// The ring position both sides of a CTA keep: the next stage and how many times the ring has wrapped.
-// Where the next stage goes, kept in step by both sides of a CTA: stages follow one another through the ring's
-// bytes (a stage that would run past the end starts over at 0) and through the kBars mbarrier pairs.
+// Where the next stage goes, kept in step by the three parties of a CTA: stages follow one another through the
+// ring's bytes (a stage that would run past the end starts over at 0) and through the kBars mbarrier pairs.
 struct Ring {
-  uint32_t count;   // stages placed so far
-  uint32_t off;     // where the next one would start
+  uint32_t off;     // where the next stage would start
+  uint32_t bar;     // byte offset of its mbarriers among their kind: 8 * (stages so far % kBars)
+  uint32_t parity;  // the phase to wait for: (stages so far / kBars) & 1
   __device__ __forceinline__ uint32_t place(uint32_t bytes) {       // byte offset of the next stage
     if (off + bytes > kRingBytes) off = 0;
     const uint32_t at = off;
     off += bytes;
     return at;
   }
-  __device__ __forceinline__ uint32_t bar() const { return 8 * (count % kBars); }        // its mbarriers' offset
-  __device__ __forceinline__ uint32_t parity() const { return (count / kBars) & 1; }    // and the phase to wait for
+  __device__ __forceinline__ void advance() {
+    bar = (bar + 8) & (8 * kBars - 1);
+    if (bar == 0) parity ^= 1;
+  }
 };
 
-// A CTA's stages of one matmul, in order: sub-panel, first tile row and number of tile rows of each.
+// A CTA's stages of one matmul, in order: sub-panel, first tile row and number of tile rows of each. Everything
+// is a scalar with a fixed place, so the walk lives in registers.
 struct Walk {
-  Segments seg;
-  int KT, ups, sq, sp, kt, left;
+  int KT, ups, segs;                       // segments left, this one included
+  int sp, kt, left;                        // where the next stage starts, and the tile rows left in this segment
+  int sp1, kt1, left1, sp2, kt2, left2;    // the segments after this one
   __device__ __forceinline__ void start(const Segments &s, int kt_count, int units_per_stage) {
-    seg = s, KT = kt_count, ups = units_per_stage, sq = 0;
-    if (seg.n > 0) sp = (int)(seg.a[0] / KT), kt = (int)(seg.a[0] % KT), left = (int)(seg.b[0] - seg.a[0]);
+    KT = kt_count, ups = units_per_stage, segs = s.n;
+    sp = (int)(s.a[0] / KT), kt = (int)(s.a[0] % KT), left = (int)(s.b[0] - s.a[0]);
+    sp1 = (int)(s.a[1] / KT), kt1 = (int)(s.a[1] % KT), left1 = (int)(s.b[1] - s.a[1]);
+    sp2 = (int)(s.a[2] / KT), kt2 = (int)(s.a[2] % KT), left2 = (int)(s.b[2] - s.a[2]);
   }
-  __device__ __forceinline__ bool more() const { return sq < seg.n; }
+  __device__ __forceinline__ bool more() const { return segs > 0; }
   __device__ __forceinline__ int rows() const { return min(min(ups, left), KT - kt); }
-  // this stage ends its sub-panel's share of the range
-  __device__ __forceinline__ bool ends_piece() const { return left == rows() || kt + rows() == KT; }
-  __device__ __forceinline__ void next() {
-    const int n = rows();
+  // a stage of n tile rows ends its sub-panel's share of the range
+  __device__ __forceinline__ bool ends_piece(int n) const { return left == n || kt + n == KT; }
+  __device__ __forceinline__ void next(int n) {
     left -= n, kt += n;
     if (kt == KT) kt = 0, sp++;
-    if (left == 0 && ++sq < seg.n) sp = (int)(seg.a[sq] / KT), kt = (int)(seg.a[sq] % KT), left = (int)(seg.b[sq] - seg.a[sq]);
+    if (left == 0) segs--, sp = sp1, kt = kt1, left = left1, sp1 = sp2, kt1 = kt2, left1 = left2;
   }
 };
 
@@ -329,16 +346,17 @@ struct Walk {
 // (the oldest stage in the ring freed by the consumers), each keeping its own books, so neither waits for the other.
 // Weights never depend on an earlier matmul: their copies go out as soon as the ring has room, lane 0 announcing
 // the bytes and lanes 0 and 1 issuing one bulk copy per weight matrix. x is the result of an earlier matmul: the x
-// warp waits (with a limit) until every CTA has reported the matmul before finished, then copies each stage's x
-// tiles with one bulk copy (an asynchronous copy costs its issuer some 250 cycles whatever its size, so the tiles
-// go whole rather than row by row). While the x warp waits, the weight warp fills the ring.
+// warp waits (with a limit) until every CTA has reported the matmuls it depends on finished, then copies each stage's
+// x tiles: whole with one bulk copy for more than 16 token rows, else the first half of each tile (token rows 0-15),
+// one copy per tile issued from as many lanes at once (an asynchronous copy costs its issuer some 250 cycles
+// whatever its size, which rules out copying row by row). While the x warp waits, the weight warp fills the ring.
 template <bool WEIGHTS>
 __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t sbase, int cta, int ctas) {
-  const uint32_t full0 = sbase + kSmFull, xfull0 = sbase + kSmXFull, empty0 = sbase + kSmEmpty, ring0 = sbase + kSmRing;
+  const uint32_t full0 = sbase + kSmFull, empty0 = sbase + kSmEmpty, ring0 = sbase + kSmRing;
   volatile uint32_t *held = reinterpret_cast<volatile uint32_t *>(smem + kSmHeld) + (WEIGHTS ? 0 : kBars);   // ring bytes of each stage in the ring
   const int lane = threadIdx.x & 31;
-  Ring ring{0, 0};
-  uint32_t oldest = 0, used = 0;        // first stage not yet known to be free; ring bytes held from there on
+  Ring ring{0, 0, 0};
+  uint32_t count = 0, oldest = 0, used = 0;   // stages placed; first stage not yet known to be free; ring bytes held from there on
   for (int i = 0; i < q.n; i++) {
     const GemvParams &p = q.op[i];
     const Geometry g = geometry(p.fmt, p.pair != 0, p.tg);
@@ -350,11 +368,12 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
     walk.start(segments_of(range_start(units, cta, active), range_start(units, cta + 1, active), KT), KT, g.ups);
     const uint8_t *w = p.w[lane < nw ? lane : 0];
     bool gate = !WEIGHTS;                 // the x warp has yet to wait for the matmul before this one
-    for (int stage_no = 0; walk.more(); walk.next(), stage_no++) {
+    for (int stage_no = 0; walk.more(); stage_no++) {
       const int n = walk.rows(), sp = walk.sp, kt = walk.kt;
+      walk.next(n);
       // room: the stage's bytes plus what is skipped when it starts over at the ring's beginning
       const uint32_t need = g.stage + (ring.off + g.stage > kRingBytes ? kRingBytes - ring.off : 0);
-      for (uint32_t spins = 0; used + need > kRingBytes || ring.count - oldest == kBars;) {
+      for (uint32_t spins = 0; used + need > kRingBytes || count - oldest == kBars;) {
         int ok = 0;
         if (lane == 0) ok = mbar_try_wait(empty0 + 8 * (oldest % kBars), (oldest / kBars) & 1, 100000u);
         if (__shfl_sync(0xFFFFFFFFu, ok, 0)) {
@@ -364,7 +383,7 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
           break;
         }
       }
-      const uint32_t b = ring.count % kBars, stage = ring0 + ring.place(g.stage);
+      const uint32_t b = count % kBars, stage = ring0 + ring.place(g.stage);
       if (lane == 0) held[b] = need;
       if (WEIGHTS) {
         const int width = min(kWC, p.TC - sp * kWC);
@@ -376,14 +395,14 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
         BT_STAGE_TRACE(1, stage_no, lane == 0);
       } else {
         if (gate) {
-          // x is the result of the launch before this one, or of the matmul before this one
+          // x may be the result of the launch before this one, or of an earlier matmul of this one: the host has
+          // worked out the last matmul this one must see finished, by every CTA
           int ok = 1;
           if (lane == 0) {
-            if (i == 0) {
-              asm volatile("griddepcontrol.wait;" ::: "memory");     // returns when the previous launch is complete and visible
-            } else {
+            asm volatile("griddepcontrol.wait;" ::: "memory");     // returns when the previous launch is complete and visible
+            if (p.wait_for >= 0) {
               uint32_t spins = 0;
-              while (ld_acquire_gpu(q.ops_done + i - 1) < ctas) {
+              while (ld_acquire_gpu(q.ops_done + p.wait_for) < ctas) {
                 if (++spins > kSpinLimit * 32) { ok = 0; break; }
                 __nanosleep(32);
               }
@@ -394,15 +413,21 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
           BT_TRACE(1, lane == 0);
         }
         BT_STAGE_TRACE(4, stage_no, lane == 0);
-        if (lane == 0) {
-          mbar_expect_tx(xfull0 + 8 * b, n * 2048);
-          bulk_g2s(stage + g.w_bytes, p.x + (size_t)kt * 2048, n * 2048, xfull0 + 8 * b);
+        if (p.tg == 4) {
+          if (lane == 0) {
+            mbar_expect_tx(full0 + 8 * b, n * 2048);
+            bulk_g2s(stage + g.w_bytes, p.x + (size_t)kt * 2048, n * 2048, full0 + 8 * b);
+          }
+        } else {
+          // up to 16 token rows: the first half of each x tile, one copy per tile from as many lanes
+          if (lane == 0) mbar_expect_tx(full0 + 8 * b, n * 1024);
+          __syncwarp();
+          if (lane < n) bulk_g2s(stage + g.w_bytes + lane * 1024, p.x + (size_t)(kt + lane) * 2048, 1024, full0 + 8 * b);
         }
         BT_STAGE_TRACE(5, stage_no, lane == 0);
         BT_STAGE_TRACE(6, stage_no, lane == 0);
       }
-      used += need, ring.count++;
-      BT_STAGE_TRACE(7, stage_no, !WEIGHTS && lane == 0);
+      used += need, count++;
     }
     BT_TRACE(5, WEIGHTS && lane == 0);
   }
@@ -410,7 +435,7 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
 
 // ---- consumers: one matmul of the queue -------------------------------------------------------------------------
 template <int FMT, int TG, bool PAIR>
-__device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Ring &ring, uint8_t *smem, uint32_t sbase, int cta, int ctas) {
+__device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, const Scratch &sc, Ring &ring, uint8_t *smem, uint32_t sbase, int cta, int ctas) {
   constexpr Geometry G = geometry(FMT, PAIR, TG);
   constexpr int ACC = 8 * TG;                                  // accumulator floats per lane
   const uint32_t full0 = sbase + kSmFull, empty0 = sbase + kSmEmpty;
@@ -441,12 +466,12 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Rin
   bool first_stage = true;
   for (int stage_no = 0; walk.more(); stage_no++) {
     const int n = walk.rows(), sp = walk.sp, col = sp * kWC + cc, done_sp = sp;
-    const bool piece_ends = walk.ends_piece();
-    walk.next();
+    const bool piece_ends = walk.ends_piece(n);
+    walk.next(n);
     const bool last_stage = !walk.more();
-    const uint32_t slot = ring.place(G.stage), bar = ring.bar();
+    const uint32_t slot = ring.place(G.stage), bar = ring.bar;
     {
-      if (!mbar_wait(full0 + bar, ring.parity(), kSpinLimit) || !mbar_wait(sbase + kSmXFull + bar, ring.parity(), kSpinLimit)) atomicExch(q.error, 2);
+      if (!mbar_wait(full0 + bar, ring.parity, kSpinLimit)) atomicExch(q.error, 2);
       BT_STAGE_TRACE(2, stage_no, threadIdx.x == 0);
       BT_TRACE(2, threadIdx.x == 0 && first_stage);
       first_stage = false;
@@ -473,7 +498,7 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Rin
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + bar);
       BT_STAGE_TRACE(3, stage_no, threadIdx.x == 0);
-      ring.count++;
+      ring.advance();
       BT_TRACE(3, threadIdx.x == 0 && last_stage);
       if (!piece_ends) continue;
 
@@ -498,11 +523,11 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Rin
       const int first = cta_of((long long)done_sp * KT, units, active), last = cta_of((long long)(done_sp + 1) * KT - 1, units, active);
       const bool finish = cta == last;        // the owner finishes the sub-panel; the others only contribute
       if (first != last) {
-        int *counter = q.counters + done_sp;
+        int *counter = sc.counters + done_sp;
         if (!finish) {
           // a contributor has one shared sub-panel that it does not own, so one slot per CTA is enough
           if (mine) {
-            float4 *slot = reinterpret_cast<float4 *>(q.partials + (size_t)cta * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
+            float4 *slot = reinterpret_cast<float4 *>(sc.partials + (size_t)cta * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
 #pragma unroll
             for (int i = 0; i < ACC / 4; i++)
               slot[i * 32 + lane] = make_float4(ACC_OF(acc, 4 * i), ACC_OF(acc, 4 * i + 1), ACC_OF(acc, 4 * i + 2), ACC_OF(acc, 4 * i + 3));
@@ -529,7 +554,7 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Rin
               float4 v[BATCH][ACC / 4];
 #pragma unroll
               for (int j = 0; j < BATCH; j++) {
-                const float4 *slot = reinterpret_cast<const float4 *>(q.partials + (size_t)(c0 + j) * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
+                const float4 *slot = reinterpret_cast<const float4 *>(sc.partials + (size_t)(c0 + j) * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
 #pragma unroll
                 for (int i = 0; i < ACC / 4; i++) v[j][i] = c0 + j < last ? __ldcg(slot + i * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
@@ -572,10 +597,10 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Rin
             int i = arg_i[lane];
             for (int c = 1; c < wcols; c++)
               if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
-            q.part_val[done_sp * 32 + lane] = v, q.part_idx[done_sp * 32 + lane] = i;
+            sc.part_val[done_sp * 32 + lane] = v, sc.part_idx[done_sp * 32 + lane] = i;
             __threadfence();
             int is_last = 0;
-            if (lane == 0) is_last = atomicAdd(q.panels_done, 1) == subpanels - 1;
+            if (lane == 0) is_last = atomicAdd(sc.panels_done, 1) == subpanels - 1;
             is_last = __shfl_sync(0xFFFFFFFFu, is_last, 0);
             if (is_last) {
               __threadfence();
@@ -583,13 +608,13 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, Rin
                 float bv = -INFINITY;
                 int bi = 0x7FFFFFFF;
                 for (int s2 = 0; s2 < subpanels; s2++) {
-                  const float ov = __ldcg(q.part_val + s2 * 32 + lane);
-                  const int oi = __ldcg(q.part_idx + s2 * 32 + lane);
+                  const float ov = __ldcg(sc.part_val + s2 * 32 + lane);
+                  const int oi = __ldcg(sc.part_idx + s2 * 32 + lane);
                   if (beats(ov, oi, bv, bi)) bv = ov, bi = oi;
                 }
                 p.arg_val[lane] = bv, p.arg_idx[lane] = bi + p.arg_base;
               }
-              if (lane == 0) *q.panels_done = 0;
+              if (lane == 0) *sc.panels_done = 0;
             }
           }
         }
@@ -613,8 +638,7 @@ __global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBars; s++) {
-      mbar_init(sbase + kSmFull + 8 * s, 1);        // the announcement of the weight bytes
-      mbar_init(sbase + kSmXFull + 8 * s, 1);       // the announcement of the x bytes
+      mbar_init(sbase + kSmFull + 8 * s, 2);        // the announcements of the weight bytes and of the x bytes
       mbar_init(sbase + kSmEmpty + 8 * s, kCW);
     }
     mbar_fence_init();
@@ -625,23 +649,24 @@ __global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid
     else produce<false>(q, smem, sbase, cta, ctas);
     return;
   }
-  Ring ring{0, 0};
+  Ring ring{0, 0, 0};
   for (int i = 0; i < q.n; i++) {
     const GemvParams &p = q.op[i];
+    const Scratch &sc = q.set[i & (q.sets - 1)];
     const int kind = (p.fmt == BT_BFP4 ? 6 : 0) + (p.pair ? 3 : 0) + (p.tg == 1 ? 0 : p.tg == 2 ? 1 : 2);
     switch (kind) {
-      case 0: consume<BT_BFP8, 1, false>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 1: consume<BT_BFP8, 2, false>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 2: consume<BT_BFP8, 4, false>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 3: consume<BT_BFP8, 1, true>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 4: consume<BT_BFP8, 2, true>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 5: consume<BT_BFP8, 4, true>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 6: consume<BT_BFP4, 1, false>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 7: consume<BT_BFP4, 2, false>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 8: consume<BT_BFP4, 4, false>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 9: consume<BT_BFP4, 1, true>(q, p, ring, smem, sbase, cta, ctas); break;
-      case 10: consume<BT_BFP4, 2, true>(q, p, ring, smem, sbase, cta, ctas); break;
-      default: consume<BT_BFP4, 4, true>(q, p, ring, smem, sbase, cta, ctas); break;
+      case 0: consume<BT_BFP8, 1, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 1: consume<BT_BFP8, 2, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 2: consume<BT_BFP8, 4, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 3: consume<BT_BFP8, 1, true>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 4: consume<BT_BFP8, 2, true>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 5: consume<BT_BFP8, 4, true>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 6: consume<BT_BFP4, 1, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 7: consume<BT_BFP4, 2, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 8: consume<BT_BFP4, 4, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 9: consume<BT_BFP4, 1, true>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      case 10: consume<BT_BFP4, 2, true>(q, p, sc, ring, smem, sbase, cta, ctas); break;
+      default: consume<BT_BFP4, 4, true>(q, p, sc, ring, smem, sbase, cta, ctas); break;
     }
     // Report this CTA done with matmul i: its results and partial sums are visible to the whole GPU before the count
     // moves. A CTA without work in a matmul reports at once, which is harmless: the count of matmul i is complete
@@ -679,6 +704,36 @@ int check_op(const char *who, int index, const bt_gemv_op &o) {
   return BT_OK;
 }
 
+// The byte ranges a matmul reads (besides its weights, which no matmul writes) and writes.
+struct Range {
+  uint64_t a, b;
+  bool meets(const Range &o) const { return a < o.b && o.a < b; }
+};
+int ranges_read(const bt_gemv_op &o, Range *r) {
+  int n = 0;
+  r[n++] = {o.x, o.x + (uint64_t)(o.K / 32) * 2048};
+  if (o.add) r[n++] = {o.add, o.add + (uint64_t)(o.N / 32) * 2048};
+  return n;
+}
+int ranges_written(const bt_gemv_op &o, Range *r) {
+  int n = 0;
+  if (o.epilogue == BT_EPI_ARGMAX) r[n++] = {o.arg_val, o.arg_val + 4ull * o.M}, r[n++] = {o.arg_idx, o.arg_idx + 4ull * o.M};
+  else r[n++] = {o.out, o.out + (uint64_t)(o.N / 32) * (o.out_dtype == BT_FP32 ? 4096 : 2048)};
+  return n;
+}
+// `later` must not start before `earlier` is complete: it reads or writes what `earlier` writes, or writes what it reads.
+bool depends(const bt_gemv_op &later, const bt_gemv_op &earlier) {
+  Range lr[2], lw[2], er[2], ew[2];
+  const int nlr = ranges_read(later, lr), nlw = ranges_written(later, lw), ner = ranges_read(earlier, er), new_ = ranges_written(earlier, ew);
+  for (int i = 0; i < new_; i++) {
+    for (int j = 0; j < nlr; j++) if (ew[i].meets(lr[j])) return true;
+    for (int j = 0; j < nlw; j++) if (ew[i].meets(lw[j])) return true;
+  }
+  for (int i = 0; i < ner; i++)
+    for (int j = 0; j < nlw; j++) if (er[i].meets(lw[j])) return true;
+  return false;
+}
+
 // Argument checks and the launches shared by the entry points. `scratch` carries the scratch pointers.
 int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Queue &scratch, uint64_t stream) {
   BT_REQUIRE(n >= 1 && ops, "%s: needs at least one matmul", who);
@@ -708,6 +763,13 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.trace = g_trace ? g_trace + (size_t)(base + i) * kTraceStride : nullptr;
       p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32;
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
+      // The last earlier matmul of this launch that this one must not overtake: one whose result it reads (x, the
+      // addend) or whose buffers it writes, or that reads what it writes; and, because the running scratch exists
+      // `sets` times, the matmul `sets` places before it.
+      p.wait_for = i - scratch.sets;
+      for (int e = i - 1; e > p.wait_for && e >= 0; e--)
+        if (depends(o, ops[base + e])) p.wait_for = e;
+      if (p.wait_for < 0) p.wait_for = -1;
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
     // It only sets up and prefetches weights until its producer threads pass griddepcontrol.wait.
@@ -723,11 +785,20 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
   return BT_OK;
 }
 
+Scratch scratch_at(unsigned char *set) {
+  Scratch s;
+  s.panels_done = reinterpret_cast<int *>(set + kSetPanelsDone), s.counters = reinterpret_cast<int *>(set + kSetCounters);
+  s.part_val = reinterpret_cast<float *>(set + kSetArgVal), s.part_idx = reinterpret_cast<int *>(set + kSetArgIdx);
+  s.partials = reinterpret_cast<float *>(set + kSetPartials);
+  return s;
+}
+
 Queue workspace_scratch(uint64_t work) {
   Queue q{};
-  q.error = as_ptr<int>(work + kWsError), q.panels_done = as_ptr<int>(work + kWsPanelsDone), q.ops_done = as_ptr<int>(work + kWsOpsDone);
-  q.counters = as_ptr<int>(work + kWsCounters), q.part_val = as_ptr<float>(work + kWsArgVal), q.part_idx = as_ptr<int>(work + kWsArgIdx);
-  q.partials = as_ptr<float>(work + kWsPartials), q.slot_floats = (int)kSlotFloatsMax;
+  unsigned char *base = as_ptr<unsigned char>(work);
+  q.error = reinterpret_cast<int *>(base + kWsError), q.ops_done = reinterpret_cast<int *>(base + kWsOpsDone);
+  q.sets = 2, q.set[0] = scratch_at(base + kWsSets), q.set[1] = scratch_at(base + kWsSets + kSetBytes);
+  q.slot_floats = (int)kSlotFloatsMax;
   return q;
 }
 
@@ -802,10 +873,12 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   // the array keeps whatever the last call left: flags and arrival counters must start at zero
   BT_CUDA(cudaMemsetAsync(base, 0, kStControlBytes, as_stream(stream)));
   Queue scratch{};
-  scratch.error = reinterpret_cast<int *>(base + kWsError), scratch.panels_done = reinterpret_cast<int *>(base + kWsPanelsDone);
-  scratch.ops_done = reinterpret_cast<int *>(base + kWsOpsDone), scratch.counters = reinterpret_cast<int *>(base + kStCounters);
-  scratch.part_val = reinterpret_cast<float *>(base + kStArgVal), scratch.part_idx = reinterpret_cast<int *>(base + kStArgIdx);
-  scratch.partials = reinterpret_cast<float *>(base + kStPartials), scratch.slot_floats = (int)kStaticSlotFloats;
+  scratch.error = reinterpret_cast<int *>(base + kWsError), scratch.ops_done = reinterpret_cast<int *>(base + kWsOpsDone);
+  scratch.sets = 1;
+  scratch.set[0].panels_done = reinterpret_cast<int *>(base + 192), scratch.set[0].counters = reinterpret_cast<int *>(base + kStCounters);
+  scratch.set[0].part_val = reinterpret_cast<float *>(base + kStArgVal), scratch.set[0].part_idx = reinterpret_cast<int *>(base + kStArgIdx);
+  scratch.set[0].partials = reinterpret_cast<float *>(base + kStPartials), scratch.set[1] = scratch.set[0];
+  scratch.slot_floats = (int)kStaticSlotFloats;
   return enqueue("bt_gemv_bfp_static", device, 1, &op, scratch, stream);
 }
 

@@ -186,6 +186,31 @@ def test_queue_longer_than_one_launch(rt):
   assert np.array_equal(h.numpy(), x)                               # x @ I, forty times
 
 
+def test_queue_of_independent_matmuls(rt):
+  # matmuls that do not read one another's results may overlap inside the launch (two in flight); some do depend
+  # (the last reads the first one's result; a dropped result's memory is handed to a later one), which the library
+  # works out from the addresses
+  rng = np.random.default_rng(41)
+  cases = [(1, 1024, 736, "bfp8"), (8, 512, 2048, "bfp4"), (20, 1024, 736, "bfp4"), (3, 2048, 512, "bfp8"), (16, 512, 1024, "bfp8"), (1, 512, 4096, "bfp4")]
+  host = [(acts(rng, m, k), weights(rng, k, n), fmt) for m, k, n, fmt in cases]
+  dev = [(upload(rt, x), upload(rt, w).cast(fmt).columns()) for x, w, fmt in host]
+  w_last = weights(rng, 736, 512)
+  tw_last = upload(rt, w_last).cast("bfp8").columns()
+  def run():
+    dropped = (dev[1][0] @ dev[1][1]).realize()
+    del dropped                                              # the allocator hands this memory to a matmul below
+    outs = [(x @ w).realize() for x, w in dev]
+    outs.append((outs[0] @ tw_last).relu().realize())        # reads the first result
+    return outs
+  separate = [t.numpy() for t in run()]
+  for _ in range(3):
+    with rt.queue(): queued = run()
+    rt.wait()
+    for got, want in zip(queued, separate): assert np.array_equal(got.numpy(), want)
+  for (x, w, fmt), got in zip(host, separate): check_matmul(got, x, None, x @ o.dequant(w, fmt), TOL_BF16)
+  check_matmul(separate[-1], separate[0], None, np.maximum(separate[0] @ o.dequant(w_last, "bfp8"), 0), TOL_BF16)
+
+
 def test_queue_is_flushed_by_a_read(rt):
   # reading a result back inside the block sends what was collected first
   rng = np.random.default_rng(6)
