@@ -334,6 +334,8 @@ struct Walk {
   __device__ __forceinline__ int rows() const { return min(min(ups, left), KT - kt); }
   // a stage of n tile rows ends its sub-panel's share of the range
   __device__ __forceinline__ bool ends_piece(int n) const { return left == n || kt + n == KT; }
+  // past `n` tile rows that end at the sub-panel's end or at the segment's
+  __device__ __forceinline__ void skip(int n) { next(n); }
   __device__ __forceinline__ void next(int n) {
     left -= n, kt += n;
     if (kt == KT) kt = 0, sp++;
@@ -464,27 +466,48 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
   const bool mine = PAIR || ck == 0;       // this warp holds sums when a sub-panel ends
   const int slab = PAIR ? warp : cc;       // and this is their place in a slot of partial sums
   bool first_stage = true;
-  for (int stage_no = 0; walk.more(); stage_no++) {
-    const int n = walk.rows(), sp = walk.sp, col = sp * kWC + cc, done_sp = sp;
-    const bool piece_ends = walk.ends_piece(n);
-    walk.next(n);
+  int stage_no = 0;
+  const int TC = p.TC;
+  uint32_t slot = 0;
+  // A stage: find its place in the ring and wait for its weights and x; when done with it, free it.
+  auto stage_begin = [&]() {
+    slot = ring.place(G.stage);
+    if (!mbar_wait(full0 + ring.bar, ring.parity, kSpinLimit)) atomicExch(q.error, 2);
+    BT_STAGE_TRACE(2, stage_no, threadIdx.x == 0);
+    BT_TRACE(2, threadIdx.x == 0 && first_stage);
+    first_stage = false;
+  };
+  auto stage_end = [&]() {
+    __syncwarp();
+    mbar_arrive_if(empty0 + ring.bar, lane == 0);
+    BT_STAGE_TRACE(3, stage_no, threadIdx.x == 0);
+    ring.advance();
+    stage_no++;
+  };
+  while (walk.more()) {
+    // one piece: the rest of this sub-panel's share of the range, as whole stages and then what is left
+    const int sp = walk.sp, col = sp * kWC + cc, done_sp = sp, width = min(kWC, TC - sp * kWC);
+    int todo = min(walk.left, KT - walk.kt);
+    walk.skip(todo);
     const bool last_stage = !walk.more();
-    const uint32_t slot = ring.place(G.stage), bar = ring.bar;
     {
-      if (!mbar_wait(full0 + bar, ring.parity, kSpinLimit)) atomicExch(q.error, 2);
-      BT_STAGE_TRACE(2, stage_no, threadIdx.x == 0);
-      BT_TRACE(2, threadIdx.x == 0 && first_stage);
-      first_stage = false;
-      if (col < p.TC) {
-        const int width = min(kWC, p.TC - sp * kWC);
-        if (n == G.ups && width == kWC) {
-          // a full stage of a full run: every offset is a compile-time constant
+      if (width == kWC) {
+        // full stages of a full run: every offset is a compile-time constant
+        for (; todo >= G.ups; todo -= G.ups) {
+          stage_begin();
 #pragma unroll
           for (int j = 0; j < G.t; j++) {
             const uint32_t row = PAIR ? j : 2 * j + ck, o = slot + (row * kWC + cc) * G.tb;
             tile_mma<FMT, TG>(lane_tile + o, lane_ex + o, lane_x + slot + row * G.xb, acc);
           }
-        } else {
+          stage_end();
+        }
+      }
+      while (todo > 0) {
+        const int n = min(G.ups, todo);
+        todo -= n;
+        stage_begin();
+        if (col < TC) {
 #pragma unroll
           for (int j = 0; j < G.t; j++) {
             const int row = PAIR ? j : 2 * j + ck;
@@ -494,13 +517,9 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
             }
           }
         }
+        stage_end();
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + bar);
-      BT_STAGE_TRACE(3, stage_no, threadIdx.x == 0);
-      ring.advance();
       BT_TRACE(3, threadIdx.x == 0 && last_stage);
-      if (!piece_ends) continue;
 
       // ---- this CTA is done with sub-panel done_sp: add the k halves, combine with other CTAs, run the epilogue ----
       if (!PAIR) {
@@ -584,14 +603,14 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
 #pragma unroll
             for (int i = 0; i < 8; i++) ACC_OF(up, 8 * r + i) = red[(cc * 8 + i) * 32 + lane];
           }
-          if (ck == 0 && col < p.TC) finish_column<TG, true>(p, acc, up, col, cc, lane, arg_v, arg_i);
-        } else if (ck == 0 && col < p.TC) {
+          if (ck == 0 && col < TC) finish_column<TG, true>(p, acc, up, col, cc, lane, arg_v, arg_i);
+        } else if (ck == 0 && col < TC) {
           finish_column<TG, false>(p, acc, acc, col, cc, lane, arg_v, arg_i);
         }
         if (!PAIR && p.epi == BT_EPI_ARGMAX) {
           // the sub-panel's best per token, then, in the last sub-panel to finish, the best over all sub-panels in order
           named_barrier(1, kCW * 32);
-          const int wcols = min(kWC, p.TC - done_sp * kWC);
+          const int wcols = min(kWC, TC - done_sp * kWC);
           if (warp == 0) {
             float v = arg_v[lane];
             int i = arg_i[lane];
@@ -734,6 +753,16 @@ bool depends(const bt_gemv_op &later, const bt_gemv_op &earlier) {
   return false;
 }
 
+// The last earlier matmul of a launch that matmul `i` of it (ops[i]; the launch starts at ops[0]) must not overtake:
+// one whose result it reads (x, the addend) or whose buffers it writes, or that reads what it writes; and, because
+// the running scratch exists `sets` times, the matmul `sets` places before it. -1: none.
+int wait_for(const bt_gemv_op *ops, int i, int sets) {
+  int w = i - sets;
+  for (int e = i - 1; e > w && e >= 0; e--)
+    if (depends(ops[i], ops[e])) w = e;
+  return w < 0 ? -1 : w;
+}
+
 // Argument checks and the launches shared by the entry points. `scratch` carries the scratch pointers.
 int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Queue &scratch, uint64_t stream) {
   BT_REQUIRE(n >= 1 && ops, "%s: needs at least one matmul", who);
@@ -763,13 +792,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.trace = g_trace ? g_trace + (size_t)(base + i) * kTraceStride : nullptr;
       p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32;
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
-      // The last earlier matmul of this launch that this one must not overtake: one whose result it reads (x, the
-      // addend) or whose buffers it writes, or that reads what it writes; and, because the running scratch exists
-      // `sets` times, the matmul `sets` places before it.
-      p.wait_for = i - scratch.sets;
-      for (int e = i - 1; e > p.wait_for && e >= 0; e--)
-        if (depends(o, ops[base + e])) p.wait_for = e;
-      if (p.wait_for < 0) p.wait_for = -1;
+      p.wait_for = wait_for(ops + base, i, scratch.sets);
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
     // It only sets up and prefetches weights until its producer threads pass griddepcontrol.wait.
@@ -833,6 +856,17 @@ int bt_gemv_workspace_bytes(int device, size_t *bytes) {
 int bt_gemv_queue(int device, int n, const bt_gemv_op *ops, uint64_t work, size_t work_bytes, uint64_t stream) {
   BT_REQUIRE(work && work % 16 == 0 && work_bytes >= kWsBytes, "bt_gemv_queue: needs %zu bytes of 16-byte aligned scratch, got %zu", kWsBytes, work_bytes);
   return enqueue("bt_gemv_queue", device, n, ops, workspace_scratch(work), stream);
+}
+
+int bt_gemv_queue_plan(int n, const bt_gemv_op *ops, int *waits) {
+  BT_REQUIRE(n >= 1 && ops && waits, "bt_gemv_queue_plan: needs at least one matmul and somewhere for the answer");
+  for (int i = 0; i < n; i++)
+    if (int s = check_op("bt_gemv_queue_plan", i, ops[i])) return s;
+  for (int i = 0; i < n; i++) {
+    const int base = i / kQueueMax * kQueueMax, w = wait_for(ops + base, i - base, 2);
+    waits[i] = w < 0 ? -1 : base + w;
+  }
+  return BT_OK;
 }
 
 int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2, uint64_t add,

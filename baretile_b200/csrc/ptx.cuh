@@ -22,6 +22,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// The same from the lanes for which `yes` holds, without a branch around it.
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, bool yes) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar), "r"((uint32_t)yes) : "memory");
+}
 // One attempt at waiting for the phase with the given parity. The thread may sleep inside the instruction for
 // up to `hint_ns` and is woken when the phase completes, so a waiting warp issues almost nothing.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {

@@ -115,17 +115,27 @@ int bt_gemv_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
                 int arg_base, uint64_t work, size_t work_bytes, uint64_t stream);
 /* ---- a queue of matmuls in one launch: the command ring the dispatcher drains (baretile/runtime.py:734-771,
  * the resident dispatcher :369-446) ----
- * Runs ops[0..n) in order, each exactly as bt_gemv_bfp would, as one kernel (one per 32 matmuls): a matmul may read
- * what any earlier one wrote (its x, its addend), as in a decode step where each result feeds the next. Between two
- * matmuls the GPU keeps streaming: the weights of the next one are fetched while the previous one finishes, and only
- * its x waits. The weights (w, w2) must not be written by an earlier matmul of the same call or by the launch right
- * before it in the stream. The fields of bt_gemv_op are bt_gemv_bfp's arguments of the same names. */
+ * Runs ops[0..n), each exactly as bt_gemv_bfp would, as one kernel (one per 32 matmuls), with the results a
+ * one-after-the-other run gives: a matmul may read what any earlier one wrote (its x, its addend), as in a decode
+ * step where each result feeds the next, and the library works out from the addresses which earlier matmuls each
+ * one has to wait for (bt_gemv_queue_plan shows the answer). Between two matmuls the GPU keeps streaming: the
+ * weights of the next ones are fetched while the previous one finishes, only x waits, and matmuls that do not
+ * depend on one another overlap (two in flight at most). The weights (w, w2) must not be written by an earlier
+ * matmul of the same call or by the launch right before it in the stream. The fields of bt_gemv_op are
+ * bt_gemv_bfp's arguments of the same names. */
 typedef struct bt_gemv_op {
   int fmt, epilogue, M, K, N, out_dtype, arg_base;
   float alpha;
   uint64_t x, w, w2, add, out, arg_val, arg_idx;
 } bt_gemv_op;
 int bt_gemv_queue(int device, int n, const bt_gemv_op *ops, uint64_t work, size_t work_bytes, uint64_t stream);
+/* What bt_gemv_queue would make each matmul wait for, without touching a device: waits[i] receives the index of the
+ * last earlier matmul that ops[i] must see finished before it starts, or -1 when it only waits for the launch
+ * before it. A matmul waits for the latest earlier one whose result it reads (x, add) or whose result buffers it
+ * writes or that reads what it writes, and never runs more than two places ahead of a matmul still in flight; a
+ * list longer than 32 is cut into launches of 32, and the first matmul of a launch waits for the whole launch
+ * before it (-1). */
+int bt_gemv_queue_plan(int n, const bt_gemv_op *ops, int *waits);
 /* ---- the matmul: fused_kernel's prefill grid (baretile/kernels.py:205-215, :470-506, grid_parts :18-39) ----
  * out[M, N] = epilogue(alpha * (a[M, K] @ W[K, N])) for many rows, on the tcgen05 tensor cores with fp32
  * accumulators in tensor memory. The weights are expanded from block float to exact bf16 inside the kernel.

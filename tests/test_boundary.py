@@ -87,3 +87,31 @@ def test_hole_allocator_merges():
   holes = [(512, 256), (0, 256), (256, 256), (2048, 64)]
   _merge_holes(holes)
   assert holes == [(0, 768), (2048, 64)]
+
+
+def test_queue_plan_follows_the_addresses(built):
+  # which earlier matmul each one of a queue waits for: worked out on the host from the buffers, no device needed
+  from baretile_b200 import _lib
+  def op(x, out, m=8, k=512, n=1024, add=0, fmt=8, epilogue=0):
+    return _lib.GemvOp(fmt=fmt, epilogue=epilogue, M=m, K=k, N=n, out_dtype=0, alpha=1.0, x=x, w=0x100000, w2=0x200000 if epilogue == 3 else 0, add=add, out=out)
+  def plan(ops):
+    arr, waits = (_lib.GemvOp * len(ops))(*ops), (ctypes.c_int * len(ops))()
+    _lib.call("bt_gemv_queue_plan", len(ops), arr, waits)
+    return list(waits)
+  A, B, C, D, E = (0x1000000 * i for i in range(1, 6))
+  # a chain: every matmul reads the one before it
+  assert plan([op(A, B), op(B, C, k=1024), op(C, D, k=1024), op(D, E, k=1024)]) == [-1, 0, 1, 2]
+  # independent matmuls: only the limit of two in flight holds them back
+  assert plan([op(A, B), op(A, C), op(A, D), op(A, E)]) == [-1, -1, 0, 1]
+  # the addend is read too; a result buffer is not overwritten while an earlier matmul may still read or write it
+  assert plan([op(A, B), op(A, C, add=B)]) == [-1, 0]
+  assert plan([op(A, B), op(C, A)]) == [-1, 0]                       # writes what the first one reads
+  assert plan([op(A, B), op(C, B)]) == [-1, 0]                       # writes what the first one writes
+  assert plan([op(A, B), op(A + 512 * 64, C, k=32)]) == [-1, -1]      # reads A's tiles past the first one's 16: no overlap with B
+  assert plan([op(A, B), op(B + 2048 * 31, C, k=32)]) == [-1, 0]      # the last tile of B
+  assert plan([op(A, B), op(B + 2048 * 32, C, k=32)]) == [-1, -1]     # just past B
+  # a list longer than one launch: the 33rd matmul starts a new launch and waits for all of the first
+  many = [op(A, B + 0x10000 * i) for i in range(34)]
+  waits = plan(many)
+  assert waits[:3] == [-1, -1, 0] and waits[31] == 29 and waits[32] == -1 and waits[33] == -1
+  with pytest.raises(ValueError, match="matmul 1: takes 1 to 32 rows"): plan([op(A, B), op(A, C, m=33)])
