@@ -72,7 +72,8 @@ constexpr size_t kSetArgIdx = kSetArgVal + 4 * 32 * kMaxSubPanels;   // int[kMax
 constexpr size_t kSetPartials = kSetArgIdx + 4 * 32 * kMaxSubPanels;
 constexpr size_t kSlotFloatsMax = 8 * 32 * 32;                   // 8 warps x up to 32 accumulators x 32 lanes
 constexpr size_t kSetBytes = kSetPartials + (size_t)kMaxCtas * kSlotFloatsMax * 4;
-constexpr size_t kWsBytes = kWsSets + 2 * kSetBytes;
+constexpr int kSets = 2;                                         // matmuls of a queue in flight at most
+constexpr size_t kWsBytes = kWsSets + kSets * kSetBytes;
 
 // The shape of a stage for one kind of matmul: format, one matrix or a gate/up pair, token groups of 8 rows.
 struct Geometry {
@@ -111,6 +112,7 @@ struct GemvParams {
   int arg_base, M, KT, TC, epi, out_fp32;
   int fmt, pair, tg;
   int wait_for;               // the matmul of the launch that must be complete before this one starts; -1: none
+  int turn;                   // CTA c takes the unit range (c + turn) % CTAs
 };
 
 // What a matmul uses while it runs: the count of finished sub-panels (argmax), the arrivals per sub-panel (both
@@ -125,9 +127,9 @@ struct Scratch {
 // finished each matmul (zero before first use; the kernel leaves them zero) and one or two sets of running scratch.
 struct Queue {
   int n;
-  int sets;                   // 2: matmuls alternate between the sets, and two may be in flight; 1: one after the other
+  int sets;                   // kSets: matmuls take the sets in turn, and as many may be in flight; 1: one after the other
   int *error, *ops_done;
-  Scratch set[2];
+  Scratch set[kSets];
   int slot_floats;            // floats between two CTAs' slots of partial sums
   GemvParams op[kQueueMax];
 };
@@ -364,10 +366,11 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
     const Geometry g = geometry(p.fmt, p.pair != 0, p.tg);
     const int KT = p.KT, nw = p.pair ? 2 : 1;
     const long long units = (long long)((p.TC + kWC - 1) / kWC) * KT;
-    const int active = (int)min((long long)ctas, units);     // a small matmul leaves the last CTAs without work
-    if (cta >= active) continue;
+    const int active = (int)min((long long)ctas, units);     // a small matmul leaves the last ranges empty
+    const int me = (cta + p.turn) % ctas;                    // the range this CTA takes in this matmul
+    if (me >= active) continue;
     Walk walk;
-    walk.start(segments_of(range_start(units, cta, active), range_start(units, cta + 1, active), KT), KT, g.ups);
+    walk.start(segments_of(range_start(units, me, active), range_start(units, me + 1, active), KT), KT, g.ups);
     const uint8_t *w = p.w[lane < nw ? lane : 0];
     bool gate = !WEIGHTS;                 // the x warp has yet to wait for the matmul before this one
     for (int stage_no = 0; walk.more(); stage_no++) {
@@ -431,7 +434,6 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
       }
       used += need, count++;
     }
-    BT_TRACE(5, WEIGHTS && lane == 0);
   }
 }
 
@@ -447,11 +449,21 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ck = warp >> 2, cc = warp & 3, tl = lane & 3;
   const int KT = p.KT, subpanels = (p.TC + kWC - 1) / kWC;
   const long long units = (long long)subpanels * KT;
-  const int active = (int)min((long long)ctas, units);       // a small matmul leaves the last CTAs without work
+  const int active = (int)min((long long)ctas, units);       // a small matmul leaves the last ranges empty
+  // The ranges go round the CTAs from matmul to matmul: the CTAs that finish shared sub-panels have more to do than
+  // the others, and it should not be the same ones every time.
+  const int me = (cta + p.turn) % ctas;
   BT_TRACE(0, threadIdx.x == 0);
-  if (cta >= active) return;
+#ifdef BT_GEMV_TRACE
+  if (p.trace && threadIdx.x == 0) {
+    unsigned sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    p.trace[blockIdx.x * 8 + 5] = sm + 1;
+  }
+#endif
+  if (me >= active) return;
   Walk walk;
-  walk.start(segments_of(range_start(units, cta, active), range_start(units, cta + 1, active), KT), KT, G.ups);
+  walk.start(segments_of(range_start(units, me, active), range_start(units, me + 1, active), KT), KT, G.ups);
 
   float acc[2][TG][4];
 // accumulator i of the lane, with i a compile-time constant after unrolling, so that acc stays in registers
@@ -540,13 +552,13 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
       }
       BT_TRACE(6, threadIdx.x == 0 && last_stage);
       const int first = cta_of((long long)done_sp * KT, units, active), last = cta_of((long long)(done_sp + 1) * KT - 1, units, active);
-      const bool finish = cta == last;        // the owner finishes the sub-panel; the others only contribute
+      const bool finish = me == last;         // the owner finishes the sub-panel; the others only contribute
       if (first != last) {
         int *counter = sc.counters + done_sp;
         if (!finish) {
           // a contributor has one shared sub-panel that it does not own, so one slot per CTA is enough
           if (mine) {
-            float4 *slot = reinterpret_cast<float4 *>(sc.partials + (size_t)cta * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
+            float4 *slot = reinterpret_cast<float4 *>(sc.partials + (size_t)me * q.slot_floats) + (size_t)slab * (ACC / 4) * 32;
 #pragma unroll
             for (int i = 0; i < ACC / 4; i++)
               slot[i * 32 + lane] = make_float4(ACC_OF(acc, 4 * i), ACC_OF(acc, 4 * i + 1), ACC_OF(acc, 4 * i + 2), ACC_OF(acc, 4 * i + 3));
@@ -671,7 +683,7 @@ __global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid
   Ring ring{0, 0, 0};
   for (int i = 0; i < q.n; i++) {
     const GemvParams &p = q.op[i];
-    const Scratch &sc = q.set[i & (q.sets - 1)];
+    const Scratch &sc = q.set[i % q.sets];
     const int kind = (p.fmt == BT_BFP4 ? 6 : 0) + (p.pair ? 3 : 0) + (p.tg == 1 ? 0 : p.tg == 2 ? 1 : 2);
     switch (kind) {
       case 0: consume<BT_BFP8, 1, false>(q, p, sc, ring, smem, sbase, cta, ctas); break;
@@ -793,6 +805,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32;
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
       p.wait_for = wait_for(ops + base, i, scratch.sets);
+      p.turn = (int)(((long long)(base + i) * 101) % ctas);
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
     // It only sets up and prefetches weights until its producer threads pass griddepcontrol.wait.
@@ -820,7 +833,8 @@ Queue workspace_scratch(uint64_t work) {
   Queue q{};
   unsigned char *base = as_ptr<unsigned char>(work);
   q.error = reinterpret_cast<int *>(base + kWsError), q.ops_done = reinterpret_cast<int *>(base + kWsOpsDone);
-  q.sets = 2, q.set[0] = scratch_at(base + kWsSets), q.set[1] = scratch_at(base + kWsSets + kSetBytes);
+  q.sets = kSets;
+  for (int s = 0; s < kSets; s++) q.set[s] = scratch_at(base + kWsSets + s * kSetBytes);
   q.slot_floats = (int)kSlotFloatsMax;
   return q;
 }
@@ -863,7 +877,7 @@ int bt_gemv_queue_plan(int n, const bt_gemv_op *ops, int *waits) {
   for (int i = 0; i < n; i++)
     if (int s = check_op("bt_gemv_queue_plan", i, ops[i])) return s;
   for (int i = 0; i < n; i++) {
-    const int base = i / kQueueMax * kQueueMax, w = wait_for(ops + base, i - base, 2);
+    const int base = i / kQueueMax * kQueueMax, w = wait_for(ops + base, i - base, kSets);
     waits[i] = w < 0 ? -1 : base + w;
   }
   return BT_OK;
@@ -911,7 +925,7 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   scratch.sets = 1;
   scratch.set[0].panels_done = reinterpret_cast<int *>(base + 192), scratch.set[0].counters = reinterpret_cast<int *>(base + kStCounters);
   scratch.set[0].part_val = reinterpret_cast<float *>(base + kStArgVal), scratch.set[0].part_idx = reinterpret_cast<int *>(base + kStArgIdx);
-  scratch.set[0].partials = reinterpret_cast<float *>(base + kStPartials), scratch.set[1] = scratch.set[0];
+  scratch.set[0].partials = reinterpret_cast<float *>(base + kStPartials);
   scratch.slot_floats = (int)kStaticSlotFloats;
   return enqueue("bt_gemv_bfp_static", device, 1, &op, scratch, stream);
 }
