@@ -169,9 +169,6 @@ __device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
 // where the lane's exponents are; xs = x tile base + 32 * g + 8 * t (g = lane / 4, t = lane % 4).
 template <int FMT, int TG>
 __device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t ex, uint32_t xs, float (&acc)[2][TG][4]) {
-#ifdef BT_NO_MATH
-  return;
-#endif
   const uint4 ev = lds128(ex);
   const uint32_t ee[4] = {ev.x, ev.y, ev.z, ev.w};
   uint2 bx[2][TG];
@@ -930,9 +927,11 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   return enqueue("bt_gemv_bfp_static", device, 1, &op, scratch, stream);
 }
 
-// Debugging aid: when `buffer` is nonzero, every later matmul writes 8 nanosecond timestamps per CTA into it
-// (start, -, first stage arrived, last stage consumed, end, last copy issued, k halves added, partial sums
-// combined); matmul i of a queue writes at buffer + i * 32 KiB. 0 turns it off. Only the trace build records.
+// Debugging aid: when `buffer` is nonzero, every later matmul writes nanosecond timestamps, 8 per CTA, into it:
+// [0] the consumers reach the matmul, [1] the x warp may copy x, [2] first stage there, [3] last stage consumed,
+// [4] done, [5] SM number + 1, [6] k halves added, [7] partial sums combined; CTA 0 adds cycle counts for its
+// first 32 stages from 8 * 2400 bytes on. Matmul i of a queue writes at buffer + i * 32 KiB. 0 turns it off. Only
+// the trace build (-DBT_GEMV_TRACE) records.
 int bt_gemv_trace(uint64_t buffer) {
   g_trace = as_ptr<unsigned long long>(buffer);
   return BT_OK;
