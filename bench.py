@@ -83,19 +83,20 @@ class Clocks:
 
 def cpu_sample(seconds_hint=15):
   """The reference's CPU path (NumPy block-float rounding + fp32 matmul, baretile/models/gpt2.py:19-30 and
-  baretile/models/llama.py:19-33,500-510) on a bounded sample of the sweep: 4096 x 14336, both formats, M = 8."""
+  baretile/models/llama.py:19-33,500-510) on a bounded sample of the sweep: 4096 x 14336, both formats, M = 1 and 8."""
   from oracle import bfp_oracle as o
   rng = np.random.default_rng(0)
-  k, n, m = 4096, 14336, 8
+  k, n = 4096, 14336
   w = o.bf16_floats(rounded(rng, (k, n), 0.02, True))
-  x = o.bf16_floats(rounded(rng, (m, k), 1.0))
   t0, total = time.perf_counter(), 0
-  for fmt in FORMATS:
-    wd = o.dequant(w, fmt)                  # unpack: the weights as the values the format holds
-    o.matmul(x, wd, "none")
-    total += algorithmic_bytes(k, n, fmt, m, False)
+  for m in (1, 8):
+    x = o.bf16_floats(rounded(rng, (m, k), 1.0))
+    for fmt in FORMATS:
+      wd = o.dequant(w, fmt)                  # unpack: the weights as the values the format holds
+      o.matmul(x, wd, "none")
+      total += algorithmic_bytes(k, n, fmt, m, False)
   dt = time.perf_counter() - t0
-  return total / dt / 1e9, dt, f"4096x14336 bfp8+bfp4, M=8: NumPy block-float dequantisation + fp32 matmul, {dt:.1f} s"
+  return total / dt / 1e9, dt, f"4096x14336 bfp8+bfp4, M=1 and 8: NumPy block-float dequantisation + fp32 matmul, {dt:.1f} s"
 
 
 def run_reference(args, rank):
@@ -222,6 +223,9 @@ def main():
       _lib.call("bt_event_elapsed_ms", dev, a, b, ctypes.byref(t))
       per[i].append(t.value)
   peak, peak_kind = peaks()
+  # DRAM read + write bytes of one 24-matmul launch, from the ncu capture summarised in profiles/bench_launch_list.md;
+  # it belongs to the full sweep only
+  traffic = 1_323_952_224 if len(work) == 24 and world == 1 else None
   table, total_t = [], 0.0
   for c, ts in zip(work, per):
     t = statistics.median(ts)
@@ -327,7 +331,7 @@ def main():
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": sum(c["xh"].nbytes for c in work), "d2h_bytes_per_step": sum(2 * c["m"] * c["n"] for c in work),
                     "ms_per_step": round(e2e_s * 1e3, 3)},
             "gpu_launches": args.steps * kernels_per_step,
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 3), "traffic": None,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 3), "traffic": traffic,
                          "of": peak_kind, "kernel": "gemv_queue_kernel: a step is one launch that runs the 24 matmuls in order; bytes per launch / launch duration averaged over the event-timed region",
                          "per_launch_events_GBps": round(per_launch_sum, 1),
                          "frac_of_spec_8TBps": round(achieved / 8000, 3)},
