@@ -134,12 +134,12 @@ struct Queue {
   GemvParams op[kQueueMax];
 };
 
+#ifdef BT_GEMV_TRACE
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-#ifdef BT_GEMV_TRACE
 #define BT_TRACE(slot, cond) do { if (p.trace && (cond)) p.trace[blockIdx.x * 8 + (slot)] = global_ns(); } while (0)
 // CTA 0 also stamps its first 64 stages of a matmul: stage wait over / copies issued (producer), data there /
 // stage consumed (consumer thread 0), at 2400 + 4 * stage + which
@@ -331,8 +331,6 @@ struct Walk {
   }
   __device__ __forceinline__ bool more() const { return segs > 0; }
   __device__ __forceinline__ int rows() const { return min(min(ups, left), KT - kt); }
-  // a stage of n tile rows ends its sub-panel's share of the range
-  __device__ __forceinline__ bool ends_piece(int n) const { return left == n || kt + n == KT; }
   // past `n` tile rows that end at the sub-panel's end or at the segment's
   __device__ __forceinline__ void skip(int n) { next(n); }
   __device__ __forceinline__ void next(int n) {
@@ -559,10 +557,13 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
 #pragma unroll
             for (int i = 0; i < ACC / 4; i++)
               slot[i * 32 + lane] = make_float4(ACC_OF(acc, 4 * i), ACC_OF(acc, 4 * i + 1), ACC_OF(acc, 4 * i + 2), ACC_OF(acc, 4 * i + 3));
-            __threadfence();
           }
+          // the barrier orders every warp's stores before thread 0's fence, which releases them with the count
           named_barrier(1, kCW * 32);
-          if (threadIdx.x == 0) atomicAdd(counter, 1);
+          if (threadIdx.x == 0) {
+            fence_gpu();
+            atomicAdd(counter, 1);
+          }
         } else {
           // wait, with a limit, until the last - first other contributors have signalled
           if (threadIdx.x == 0) {
@@ -572,12 +573,12 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
               __nanosleep(64);
             }
             *counter = 0;                      // ready for the next matmul
+            fence_gpu();                       // what follows the barrier, in any warp, sees the contributors' sums
           }
           named_barrier(1, kCW * 32);
           if (mine) {
-            __threadfence();
             // this CTA's own sums first, then the others' in CTA order: the result does not depend on timing
-            constexpr int BATCH = ACC <= 16 ? 4 : 2;   // contributors whose loads are in flight together
+            constexpr int BATCH = ACC <= 8 ? 5 : ACC <= 16 ? 3 : 2;   // contributors whose loads are in flight together
             for (int c0 = first; c0 < last; c0 += BATCH) {
               float4 v[BATCH][ACC / 4];
 #pragma unroll
@@ -626,12 +627,12 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
             for (int c = 1; c < wcols; c++)
               if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
             sc.part_val[done_sp * 32 + lane] = v, sc.part_idx[done_sp * 32 + lane] = i;
-            __threadfence();
+            fence_gpu();
             int is_last = 0;
             if (lane == 0) is_last = atomicAdd(sc.panels_done, 1) == subpanels - 1;
             is_last = __shfl_sync(0xFFFFFFFFu, is_last, 0);
             if (is_last) {
-              __threadfence();
+              fence_gpu();
               if (lane < p.M) {
                 float bv = -INFINITY;
                 int bi = 0x7FFFFFFF;
@@ -702,9 +703,9 @@ __global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid
     // the last matmul finds every producer past its last look at the counts, and zeroes them for the next launch.
     // The counts are shared with the launch before this one, which may still be running (this launch may start
     // early): a CTA without work in the first matmul must not report before that launch is complete.
-    __threadfence();
     named_barrier(1, kCW * 32);
     if (threadIdx.x == 0) {
+      fence_gpu();
       if (i == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
       if (atomicAdd(q.ops_done + i, 1) == ctas - 1 && i == q.n - 1)
         for (int j = 0; j < q.n; j++) q.ops_done[j] = 0;

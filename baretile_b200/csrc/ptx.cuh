@@ -146,6 +146,11 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 
+// Release / acquire fence at GPU scope: orders this thread's earlier writes before its later signal, or its earlier
+// look at a signal before its later reads. Lighter than the sequentially consistent __threadfence().
+__device__ __forceinline__ void fence_gpu() {
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
 // A load that sees everything another thread of the GPU released before the value it returns was stored.
 __device__ __forceinline__ int ld_acquire_gpu(const int *p) {
   int v;
