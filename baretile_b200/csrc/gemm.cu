@@ -62,10 +62,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 // Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, N = 256, M = 128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
-template <int HI>
-__device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
-  return prmt(ew, 0u, HI ? 0x4342u : 0x4140u) * 128u + 0x1F801F80u;   // bf16 lanes 2^(e - 64)
-}
 __device__ __forceinline__ float silu(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 __device__ __forceinline__ uint32_t bf16_half_up(float v) { return (__float_as_uint(v) + 0x8000u) >> 16; }
 

@@ -158,12 +158,6 @@ __device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
   return b;
 }
 
-// bf16 lanes 2^(e + 63 - 127) for two exponent bytes of `ew` (bytes 0,1 for HI = 0; bytes 2,3 for HI = 1).
-template <int HI>
-__device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
-  return prmt(ew, 0u, HI ? 0x4342u : 0x4140u) * 128u + 0x1F801F80u;
-}
-
 // One weight tile times the staged x tile, added into acc[ng][tg][4]. `tile`, `ex` and `xs` are shared-memory
 // addresses that already include the lane's own offsets: tile = tile base + 16 * lane; ex = tile base + 16 * t,
 // where the lane's exponents are; xs = x tile base + 32 * g + 8 * t (g = lane / 4, t = lane % 4).

@@ -5,7 +5,10 @@
 // contiguous range. Inside a tile the 64 exponent bytes still come first, then the values, but both are
 // permuted so that each lane of a warp fetches exactly the bytes of its MMA fragment with 128-bit loads:
 //
-//   exponents  position t*16 + face*4 + kk            holds the exponent of datum row k = 4t + kk of face `face`
+//   exponents  position t*16 + face*4 + j             holds the exponent of datum row k = 4t + kk of face `face`,
+//              j = 0, 1, 2, 3 for kk = 0, 2, 1, 3: a lane's word then has the exponents of its first k pair in bytes
+//              0 and 2 and of its second pair in bytes 1 and 3, so one mask and one multiply-add turn each pair
+//              into two bf16 scale lanes (scale_pair below)
 //   bfp8       position 64 + h*512 + lane*16 + fs*8 + ns*4 + kk
 //              holds datum (k = 16h + 4t + kk, n = 16fs + 2g + ns), lane = 4g + t
 //   bfp4       position 64 + lane*16 + h*8 + fs*4 + kk
@@ -24,7 +27,7 @@ constexpr int kPanel = 4;  // tile columns in a run
 // Position in the streamed tile of canonical byte c.
 template <int FMT>
 __host__ __device__ inline int stream_pos(int c) {
-  if (c < 64) return (c % 16 / 4) * 16 + (c / 16) * 4 + c % 4;
+  if (c < 64) return (c % 16 / 4) * 16 + (c / 16) * 4 + ((c & 1) << 1 | (c >> 1 & 1));
   int i = c - 64;
   if (FMT == BT_BFP8) {
     int face = i / 256, k = i / 16 % 16, n = i % 16;
@@ -35,6 +38,19 @@ __host__ __device__ inline int stream_pos(int c) {
   int lane = g * 4 + k / 4;
   return 64 + lane * 16 + (face / 2) * 8 + (face % 2) * 4 + k % 4;
 }
+
+#ifdef __CUDACC__
+// bf16 lanes 2^(e - 64) for two exponent bytes of a lane's exponent word `ew`: bytes 0 and 2 (HI = 0, the lane's
+// first k pair) or bytes 1 and 3 (HI = 1, its second pair). e << 7 is the exponent field, 0x1F80 = 63 << 7 the bias
+// shift. Written as multiply-adds so that they run on the FMA pipe, which the dequantisation leaves mostly idle.
+template <int HI>
+__device__ __forceinline__ uint32_t scale_pair(uint32_t ew) {
+  uint32_t s;
+  if (HI) asm("mad.hi.u32 %0, %1, 0x80000000, 0x1F801F80;" : "=r"(s) : "r"(ew & 0xFF00FF00u));   // (bytes >> 1) + bias
+  else asm("mad.lo.u32 %0, %1, 128, 0x1F801F80;" : "=r"(s) : "r"(ew & 0x00FF00FFu));
+  return s;
+}
+#endif
 
 // Index, in tiles, of tile (ti, tj) of a tr x tc matrix in the streamed order.
 __host__ __device__ inline size_t stream_tile_index(int ti, int tj, int tr, int tc) {

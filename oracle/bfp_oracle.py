@@ -153,14 +153,15 @@ def stream_perm(dtype):
   canonical byte stream_perm[p]. It is defined by this backend (the reference's columns() is likewise a
   pure permutation that reads back unchanged, baretile/kernels.py:1455-1481).
 
-  Exponents: position t*16 + face*4 + kk holds the exponent of run face*16 + 4t + kk.
+  Exponents: position t*16 + face*4 + j holds the exponent of run face*16 + 4t + kk, j = 0, 1, 2, 3 for
+  kk = 0, 2, 1, 3.
   bfp8 values: position 64 + h*512 + lane*16 + fs*8 + ns*4 + kk, with lane = g*4 + t, holds datum
   (k = 16h + 4t + kk, n = 16fs + 2g + ns). bfp4 values: position 64 + lane*16 + h*8 + fs*4 + kk holds the
   byte with datums (k = 16h + 4t + kk, n = 16fs + 2g) and (…, n + 1)."""
   perm = np.zeros(tile_bytes(dtype), np.int64)
   for t in range(4):
     for face in range(4):
-      for kk in range(4): perm[t * 16 + face * 4 + kk] = face * 16 + 4 * t + kk
+      for kk in range(4): perm[t * 16 + face * 4 + (0, 2, 1, 3)[kk]] = face * 16 + 4 * t + kk
   for h in range(2):
     for g in range(8):
       for t in range(4):
