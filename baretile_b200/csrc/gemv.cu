@@ -368,11 +368,13 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
       // room: the stage's bytes plus what is skipped when it starts over at the ring's beginning
       const uint32_t need = g.stage + (ring.off + g.stage > kRingBytes ? kRingBytes - ring.off : 0);
       for (uint32_t spins = 0; used + need > kRingBytes || count - oldest == kBars;) {
+        // looking in a loop rather than sleeping in the instruction: a sleeper is woken some hundreds of ns late, and
+        // this latency is on the ring's critical path; the two producer warps are 2 of 20, so the polls are cheap
         int ok = 0;
-        if (lane == 0) ok = mbar_try_wait(empty0 + 8 * (oldest % kBars), (oldest / kBars) & 1, 100000u);
+        if (lane == 0) ok = mbar_test(empty0 + 8 * (oldest % kBars), (oldest / kBars) & 1);
         if (__shfl_sync(0xFFFFFFFFu, ok, 0)) {
           used -= held[oldest % kBars], oldest++;
-        } else if (++spins > kSpinLimit) {
+        } else if (++spins > kSpinLimit * 4096) {
           if (lane == 0) atomicExch(q.error, 1);
           break;
         }

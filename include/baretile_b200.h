@@ -106,7 +106,9 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
  *          arg_val[M] (fp32) / arg_idx[M] (int32) receive each row's largest value and its first
  *          column (topk_kernel's tie rule, baretile/kernels.py:1173-1231), index + arg_base.
  *   work   scratch of at least bt_gemv_workspace_bytes() bytes, zeroed once before first use;
- *          launches that share it must not overlap.
+ *          launches that share it go on one stream (where they may overlap at their edges: a launch
+ *          fetches weights while the one before it finishes, and touches the scratch only after it).
+ *          The weights must not be written by the launch right before it in the stream.
  * Products are exact, sums are fp32, outputs round half up to bf16 like the packer
  * (docs/compiler.md, "Matmul precision"). */
 int bt_gemv_workspace_bytes(int device, size_t *bytes);
