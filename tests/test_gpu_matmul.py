@@ -211,6 +211,39 @@ def test_queue_of_independent_matmuls(rt):
   check_matmul(separate[-1], separate[0], None, np.maximum(separate[0] @ o.dequant(w_last, "bfp8"), 0), TOL_BF16)
 
 
+def test_queue_random_programs(rt):
+  # random lists of matmuls, some reading earlier results, mixed formats, row counts, pairs and epilogues: one queue
+  # launch must give the bits that one launch per matmul gives, whatever overlaps inside
+  rng = np.random.default_rng(77)
+  dims = [256, 512, 736, 1024]
+  weights_by_shape = {}
+  def weight(k, n, fmt):
+    key = (k, n, fmt, int(rng.integers(2)))
+    if key not in weights_by_shape: weights_by_shape[key] = upload(rt, weights(rng, k, n) * 2).cast(fmt).columns()
+    return weights_by_shape[key]
+  for program in range(12):
+    m = int(rng.choice([1, 2, 8, 9, 16, 17, 32]))
+    steps, width = [], int(rng.choice(dims))
+    x0 = upload(rt, acts(rng, m, width))
+    for _ in range(int(rng.integers(3, 14))):
+      src = int(rng.integers(-1, len(steps)))          # -1: the program's input, else an earlier result
+      k = width if src < 0 else steps[src][2]
+      n, fmt, kind = int(rng.choice(dims)), str(rng.choice(["bfp8", "bfp4"])), str(rng.choice(["none", "relu", "silu", "glu"]))
+      steps.append((src, (weight(k, n, fmt), weight(k, n, fmt) if kind == "glu" else None, kind), n))
+    def run():
+      outs = []
+      for src, (w, w2, kind), _ in steps:
+        x = x0 if src < 0 else outs[src]
+        y = x @ w
+        y = y.relu() if kind == "relu" else y.silu() if kind == "silu" else y.silu() * (x @ w2) if kind == "glu" else y
+        outs.append(y.realize())
+      return outs
+    separate = [t.numpy() for t in run()]
+    with rt.queue(): queued = run()
+    rt.wait()
+    for i, (got, want) in enumerate(zip(queued, separate)): assert np.array_equal(got.numpy(), want, equal_nan=True), (program, i, m, steps[i][0], steps[i][1][2])
+
+
 def test_queue_is_flushed_by_a_read(rt):
   # reading a result back inside the block sends what was collected first
   rng = np.random.default_rng(6)
