@@ -115,3 +115,40 @@ def test_queue_plan_follows_the_addresses(built):
   waits = plan(many)
   assert waits[:3] == [-1, -1, 0] and waits[31] == 29 and waits[32] == -1 and waits[33] == -1
   with pytest.raises(ValueError, match="matmul 1: takes 1 to 32 rows"): plan([op(A, B), op(A, C, m=33)])
+
+
+def test_queue_collects_matmuls_and_flushes_in_order(monkeypatch):
+  # host logic of Runtime.queue(): matmuls are collected, anything else that needs the stream sends them first, the
+  # block's end sends the rest; the C-ABI calls are captured instead of made, so no device is needed
+  from baretile_b200 import _lib, runtime
+  calls = []
+  def fake_call(name, *args):
+    if name == "bt_gemv_queue":
+      n, arr = args[1], args[2]
+      calls.append((name, [(arr[i].fmt, arr[i].epilogue, arr[i].M, arr[i].K, arr[i].N, arr[i].x, arr[i].w, arr[i].w2, arr[i].add, arr[i].out, arr[i].out_dtype,
+                            arr[i].arg_val, arr[i].arg_idx, arr[i].arg_base, round(arr[i].alpha, 3)) for i in range(n)]))
+    else: calls.append((name, args))
+  monkeypatch.setattr(_lib, "call", fake_call)
+  rt = runtime.Runtime.__new__(runtime.Runtime)
+  rt.active, rt.device, rt.stream, rt.launches, rt.sent, rt.log, rt.pending, rt.timing, rt.work, rt.work_bytes = True, 0, 7, 0, {}, None, None, False, 4096, 1 << 20
+  def matmul(x, out, epilogue=0, w2=0, alpha=1.0):
+    rt.launch("bt_gemv_bfp", (8, epilogue, 4, 512, 1024, x, 0x1000, w2, 0, ctypes.c_float(alpha), out, 0, 0, 0, 0, rt.work, rt.work_bytes), name="matmul")
+  matmul(0x10, 0x20)                                                  # outside a queue: sent at once
+  assert [c[0] for c in calls] == ["bt_gemv_bfp"]
+  calls.clear()
+  with rt.queue():
+    matmul(0x10, 0x20)
+    matmul(0x20, 0x30, epilogue=3, w2=0x2000, alpha=0.5)
+    assert calls == []                                               # nothing has left yet
+    rt.launch("bt_untilize", (2, 0x30, 0x40, 1, 4, 1024), name="readback")
+    matmul(0x40, 0x50)
+  assert [c[0] for c in calls] == ["bt_gemv_queue", "bt_untilize", "bt_gemv_queue"]
+  assert calls[0][1] == [(8, 0, 4, 512, 1024, 0x10, 0x1000, 0, 0, 0x20, 0, 0, 0, 0, 1.0), (8, 3, 4, 512, 1024, 0x20, 0x1000, 0x2000, 0, 0x30, 0, 0, 0, 0, 0.5)]
+  assert len(calls[2][1]) == 1 and calls[2][1][0][5] == 0x40
+  assert rt.launches == 5 and rt.pending is None
+  calls.clear()
+  with pytest.raises(KeyError):
+    with rt.queue():
+      matmul(0x10, 0x20)
+      raise KeyError("the block fails")
+  assert calls == [] and rt.pending is None                          # a failed block sends nothing

@@ -244,6 +244,27 @@ def test_queue_random_programs(rt):
     for i, (got, want) in enumerate(zip(queued, separate)): assert np.array_equal(got.numpy(), want, equal_nan=True), (program, i, m, steps[i][0], steps[i][1][2])
 
 
+def test_queue_with_addend_scale_fp32_and_pick(rt):
+  # the other epilogues inside one queue: an addend that is an earlier result, a scale, an fp32 result, the greedy pick
+  rng = np.random.default_rng(9)
+  m, k, n = 5, 512, 1024
+  x, w1, w2, wv = acts(rng, m, k), weights(rng, k, n), weights(rng, k, n), weights(rng, n, 4000 // 32 * 32)
+  tx, t1, t2, tv = upload(rt, x), upload(rt, w1).cast("bfp8").columns(), upload(rt, w2).cast("bfp4").columns(), upload(rt, wv).cast("bfp8").columns()
+  def run():
+    a = (tx @ t1).realize()
+    b = ((tx @ t2) * 0.5 + a).relu().realize()                     # reads a as its addend
+    c = b.matmul(tv, dtype="fp32").realize()
+    values, ids = (b @ tv).topk(1)
+    return a, b, c, values, ids
+  separate = [t.numpy() for t in run()]
+  with rt.queue(): queued = run()
+  rt.wait()
+  for got, want in zip(queued, separate): assert np.array_equal(got.numpy(), want)
+  a, b = separate[0], separate[1]
+  check_matmul(b, x, None, np.maximum(0.5 * (x @ o.dequant(w2, "bfp4")) + a, 0), TOL_BF16)
+  assert np.array_equal(separate[4][:, 0], o.argmax(separate[2]))
+
+
 def test_queue_is_flushed_by_a_read(rt):
   # reading a result back inside the block sends what was collected first
   rng = np.random.default_rng(6)
