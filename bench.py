@@ -313,15 +313,15 @@ def main():
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
       for gather in (True, False):
         fn = lambda: mlp.forward(xs, gather=gather)
-        for _ in range(3): fn()
-        ms_ = timed(fn, 10) / 10
+        for _ in range(5): fn()
+        ms_ = statistics.median(timed(fn, 5) / 5 for _ in range(4))      # a median: the first collective of a size may set up connections
         total = 3 * (K3 // 32) * (N3 // 32) * TILE["bfp4"]
         sharded["mlp"].append({"M": m, "all_gather": gather, "us": round(ms_ * 1e3, 1), "GBps_all_ranks": round(total / (ms_ * 1e-3) / 1e9, 1)})
     for m in (1, 4, 8):
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
       fn = lambda: head.pick(xs)
-      for _ in range(3): fn()
-      ms_ = timed(fn, 10) / 10
+      for _ in range(5): fn()
+      ms_ = statistics.median(timed(fn, 5) / 5 for _ in range(4))
       total = (K3 // 32) * (V4 // 32) * TILE["bfp8"]
       sharded["head"].append({"M": m, "us": round(ms_ * 1e3, 1), "GBps_all_ranks": round(total / (ms_ * 1e-3) / 1e9, 1)})
     sharded["note"] = ("configs[3]: gate/up [8192,28672] bfp4 split over N, down [28672,8192] split over K, all-reduce of fp32 partials, with or "
