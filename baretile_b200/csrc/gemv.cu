@@ -6,11 +6,12 @@
 //
 // A queue. In decode one matmul's result is the next one's x, so between two of them the GPU has nothing to read
 // unless the next weights are already on their way. The kernel therefore takes a list of matmuls (up to kQueueMax
-// per launch) and runs them in order with the same persistent CTAs. The producer warp of a CTA walks the whole
-// list: weight copies depend on nothing and go out as soon as the ring has room, across the boundary between two
-// matmuls. Only the consumers wait: they read x straight from global memory (L2), and not before every CTA has
-// reported the previous matmul finished (a counter per matmul in global memory, read with acquire semantics).
-// While that report travels, the ring fills with the next weights.
+// per launch) and runs them in order with the same persistent CTAs. The weight warp of a CTA walks the whole list:
+// weight copies depend on nothing and go out as soon as the ring has room, across the boundary between two matmuls.
+// Only x waits: the x warp copies a matmul's activations once every CTA has reported the matmuls it depends on
+// finished (a counter per matmul in global memory, read with acquire semantics; the host works out the dependences
+// from the buffer addresses, and matmuls that do not depend on one another overlap, two in flight at most). While
+// that report travels, the ring fills with the next weights.
 //
 // Decomposition ("stream-K"). A weight matrix is cut into sub-panels of 4 tile columns (one run of the streaming
 // layout). A unit is one tile row of one sub-panel. Units are numbered sub-panel by sub-panel and dealt out in
@@ -20,8 +21,9 @@
 // counter (with a limit), adds the partials in CTA order, so results do not depend on timing, and runs the
 // epilogue. Contributors never wait, so the owner's wait always ends; it is bounded all the same.
 //
-// Inside a CTA: warp 8 is the producer. It waits for room in the ring, announces the stage's bytes to the stage's
-// mbarrier and issues one bulk copy per weight matrix. Stages are as large as the matmul's kind wants and follow
+// Inside a CTA: warps 8 and 9 are the producers. Warp 8 waits for room in the ring, announces the stage's weight
+// bytes to the stage's mbarrier and issues one bulk copy per weight matrix; warp 9 does the same for the stage's x
+// tiles once the matmuls this one depends on are finished. Stages are as large as the matmul's kind wants and follow
 // one another through the ring's bytes; 16 mbarrier pairs go round with them. The 8 consumer
 // warps form a 2 x 4 grid: warp (ck, cc) takes column cc of the sub-panel; for one weight matrix ck picks every
 // other tile row of the stage (the two halves are added through shared memory when the sub-panel ends), for a
@@ -802,7 +804,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.turn = (int)(((long long)(base + i) * 101) % ctas);
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
-    // It only sets up and prefetches weights until its producer threads pass griddepcontrol.wait.
+    // It only sets up and prefetches weights until its x warps pass griddepcontrol.wait.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = kSmemBytes, cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
