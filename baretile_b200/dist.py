@@ -32,12 +32,12 @@ def split_tiles(extent, world, rank):
 
 def combine_argmax(values, indices):
   """Per row, the best of each rank's candidate: values and indices are [world, M]. The larger value wins; of equal
-  values the lower index; -0 equals 0."""
+  values the lower index; -0 equals 0; a NaN never wins. A handful of whole-array operations whatever the world size."""
   values, indices = torch.as_tensor(values), torch.as_tensor(indices)
-  best_v, best_i = values[0].clone(), indices[0].clone()
-  for r in range(1, values.shape[0]):
-    take = (values[r] > best_v) | ((values[r] == best_v) & (indices[r] < best_i))
-    best_v, best_i = torch.where(take, values[r], best_v), torch.where(take, indices[r], best_i)
+  values = torch.nan_to_num(values, nan=float("-inf"), posinf=float("inf"), neginf=float("-inf"))
+  best_v = values.max(dim=0).values
+  far = torch.iinfo(indices.dtype).max
+  best_i = torch.where(values == best_v, indices, torch.full_like(indices, far)).min(dim=0).values
   return best_v, best_i
 
 
