@@ -36,6 +36,7 @@
 #include "ptx.cuh"
 #include "stream_layout.cuh"
 #include <cstring>
+#include <cstdlib>
 
 using namespace bt;
 
@@ -115,6 +116,7 @@ struct GemvParams {
   int fmt, pair, tg;
   int wait_for;               // the matmul of the launch that must be complete before this one starts; -1: none
   int turn;                   // CTA c takes the unit range (c + turn) % CTAs
+  int per;                    // units per range when ranges are cut to fit the sub-panels; 0: equal shares of all CTAs
 };
 
 // What a matmul uses while it runs: the count of finished sub-panels (argmax), the arrivals per sub-panel (both
@@ -151,12 +153,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
 #define BT_STAGE_TRACE(which, stage, cond) do { } while (0)
 #endif
 
-__host__ __device__ __forceinline__ long long range_start(long long units, int b, int ctas) { return units * b / ctas; }
+// Where range b of `ctas` starts: equal shares, or with `per` > 0 shares of exactly `per` units (the last one shorter).
+__host__ __device__ __forceinline__ long long range_start(long long units, int b, int ctas, int per) {
+  return per > 0 ? min((long long)b * per, units) : units * b / ctas;
+}
 // The CTA whose (non-empty) range holds unit u.
-__device__ __forceinline__ int cta_of(long long u, long long units, int ctas) {
+__device__ __forceinline__ int cta_of(long long u, long long units, int ctas, int per) {
+  if (per > 0) return (int)(u / per);
   int b = (int)(u * ctas / units);
-  while (b + 1 < ctas && range_start(units, b + 1, ctas) <= u) b++;
-  while (b > 0 && range_start(units, b, ctas) > u) b--;
+  while (b + 1 < ctas && range_start(units, b + 1, ctas, 0) <= u) b++;
+  while (b > 0 && range_start(units, b, ctas, 0) > u) b--;
   return b;
 }
 
@@ -357,11 +363,11 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
     const Geometry g = geometry(p.fmt, p.pair != 0, p.tg);
     const int KT = p.KT, nw = p.pair ? 2 : 1;
     const long long units = (long long)((p.TC + kWC - 1) / kWC) * KT;
-    const int active = (int)min((long long)ctas, units);     // a small matmul leaves the last ranges empty
+    const int active = p.per > 0 ? (int)((units + p.per - 1) / p.per) : (int)min((long long)ctas, units);   // the other ranges are empty
     const int me = (cta + p.turn) % ctas;                    // the range this CTA takes in this matmul
     if (me >= active) continue;
     Walk walk;
-    walk.start(segments_of(range_start(units, me, active), range_start(units, me + 1, active), KT), KT, g.ups);
+    walk.start(segments_of(range_start(units, me, active, p.per), range_start(units, me + 1, active, p.per), KT), KT, g.ups);
     const uint8_t *w = p.w[lane < nw ? lane : 0];
     bool gate = !WEIGHTS;                 // the x warp has yet to wait for the matmul before this one
     for (int stage_no = 0; walk.more(); stage_no++) {
@@ -442,7 +448,7 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ck = warp >> 2, cc = warp & 3, tl = lane & 3;
   const int KT = p.KT, subpanels = (p.TC + kWC - 1) / kWC;
   const long long units = (long long)subpanels * KT;
-  const int active = (int)min((long long)ctas, units);       // a small matmul leaves the last ranges empty
+  const int active = p.per > 0 ? (int)((units + p.per - 1) / p.per) : (int)min((long long)ctas, units);   // the other ranges are empty
   // The ranges go round the CTAs from matmul to matmul: the CTAs that finish shared sub-panels have more to do than
   // the others, and it should not be the same ones every time.
   const int me = (cta + p.turn) % ctas;
@@ -456,7 +462,7 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
 #endif
   if (me >= active) return;
   Walk walk;
-  walk.start(segments_of(range_start(units, me, active), range_start(units, me + 1, active), KT), KT, G.ups);
+  walk.start(segments_of(range_start(units, me, active, p.per), range_start(units, me + 1, active, p.per), KT), KT, G.ups);
 
   float acc[2][TG][4];
 // accumulator i of the lane, with i a compile-time constant after unrolling, so that acc stays in registers
@@ -544,7 +550,7 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
         }
       }
       BT_TRACE(6, threadIdx.x == 0 && last_stage);
-      const int first = cta_of((long long)done_sp * KT, units, active), last = cta_of((long long)(done_sp + 1) * KT - 1, units, active);
+      const int first = cta_of((long long)done_sp * KT, units, active, p.per), last = cta_of((long long)(done_sp + 1) * KT - 1, units, active, p.per);
       const bool finish = me == last;         // the owner finishes the sub-panel; the others only contribute
       if (first != last) {
         int *counter = sc.counters + done_sp;
@@ -771,6 +777,22 @@ int wait_for(const bt_gemv_op *ops, int i, int sets) {
   return w < 0 ? -1 : w;
 }
 
+// Units per CTA such that range boundaries fall on sub-panel boundaries (a share that divides a sub-panel's K tiles,
+// or a whole number of sub-panels), when that keeps at least 85 % of the CTAs busy; else 0: equal shares of all CTAs,
+// whose ranges straddle sub-panels. With fitted shares a CTA has one piece per matmul instead of up to three, and
+// a sub-panel's partial sums come from fewer CTAs.
+int aligned_share(int KT, int subpanels, int ctas) {
+  if (getenv("BT_NO_ALIGN")) return 0;
+  const long long units = (long long)subpanels * KT;
+  const int least = (int)((units + ctas - 1) / ctas);
+  for (int d = least; d <= 4 * least && d <= units; d++) {
+    if (KT % d != 0 && d % KT != 0) continue;
+    const long long busy = (units + d - 1) / d;
+    return busy * 100 >= (long long)(getenv("BT_ALIGN_PCT") ? atoi(getenv("BT_ALIGN_PCT")) : 85) * ctas ? d : 0;
+  }
+  return 0;
+}
+
 // Argument checks and the launches shared by the entry points. `scratch` carries the scratch pointers.
 int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Queue &scratch, uint64_t stream) {
   BT_REQUIRE(n >= 1 && ops, "%s: needs at least one matmul", who);
@@ -802,6 +824,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
       p.wait_for = wait_for(ops + base, i, scratch.sets);
       p.turn = (int)(((long long)(base + i) * 101) % ctas);
+      p.per = aligned_share(p.KT, (p.TC + kWC - 1) / kWC, ctas);
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
     // It only sets up and prefetches weights until its x warps pass griddepcontrol.wait.
