@@ -15,8 +15,9 @@
 //
 // Decomposition ("stream-K"). A weight matrix is cut into sub-panels of 4 tile columns (one run of the streaming
 // layout). A unit is one tile row of one sub-panel. Units are numbered sub-panel by sub-panel and dealt out in
-// equal contiguous ranges to the CTAs (two per SM), so every SM streams the same number of bytes whatever the
-// shape. A sub-panel that several CTAs share is finished by the CTA that holds its last tile row: the others write
+// contiguous ranges to the CTAs (two per SM): equal shares of all CTAs, so every SM streams the same number of bytes
+// whatever the shape, or, where that keeps most CTAs busy, shares cut so that ranges end where sub-panels end. A
+// sub-panel that several CTAs share is finished by the CTA that holds its last tile row: the others write
 // their fp32 partial sums to scratch and bump a counter; the owner, which takes that sub-panel last, waits for the
 // counter (with a limit), adds the partials in CTA order, so results do not depend on timing, and runs the
 // epilogue. Contributors never wait, so the owner's wait always ends; it is bounded all the same.
@@ -36,7 +37,6 @@
 #include "ptx.cuh"
 #include "stream_layout.cuh"
 #include <cstring>
-#include <cstdlib>
 
 using namespace bt;
 
@@ -778,17 +778,16 @@ int wait_for(const bt_gemv_op *ops, int i, int sets) {
 }
 
 // Units per CTA such that range boundaries fall on sub-panel boundaries (a share that divides a sub-panel's K tiles,
-// or a whole number of sub-panels), when that keeps at least 85 % of the CTAs busy; else 0: equal shares of all CTAs,
+// or a whole number of sub-panels), when that keeps at least 70 % of the CTAs busy; else 0: equal shares of all CTAs,
 // whose ranges straddle sub-panels. With fitted shares a CTA has one piece per matmul instead of up to three, and
 // a sub-panel's partial sums come from fewer CTAs.
 int aligned_share(int KT, int subpanels, int ctas) {
-  if (getenv("BT_NO_ALIGN")) return 0;
   const long long units = (long long)subpanels * KT;
   const int least = (int)((units + ctas - 1) / ctas);
   for (int d = least; d <= 4 * least && d <= units; d++) {
     if (KT % d != 0 && d % KT != 0) continue;
     const long long busy = (units + d - 1) / d;
-    return busy * 100 >= (long long)(getenv("BT_ALIGN_PCT") ? atoi(getenv("BT_ALIGN_PCT")) : 85) * ctas ? d : 0;
+    return busy * 100 >= 70LL * ctas ? d : 0;
   }
   return 0;
 }
