@@ -781,7 +781,8 @@ int wait_for(const bt_gemv_op *ops, int i, int sets) {
 // or a whole number of sub-panels), when that keeps at least the given percentage of the CTAs busy; else 0: equal
 // shares of all CTAs, whose ranges straddle sub-panels. With fitted shares a CTA has one piece per matmul instead of
 // up to three, and a sub-panel's partial sums come from fewer CTAs. Inside a queue the CTAs left without a share go
-// on to the next matmul, so 70 % is enough there; the last matmul of a launch has nothing behind it and wants 90 %.
+// on to the next matmul. The choice depends on the shape only, never on a matmul's place in a queue: the way the sums
+// are grouped, and with it the last bit of a result, must not change with how matmuls are batched.
 int aligned_share(int KT, int subpanels, int ctas, int least_busy_percent) {
   const long long units = (long long)subpanels * KT;
   const int least = (int)((units + ctas - 1) / ctas);
@@ -824,7 +825,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
       p.wait_for = wait_for(ops + base, i, scratch.sets);
       p.turn = (int)(((long long)(base + i) * 101) % ctas);
-      p.per = aligned_share(p.KT, (p.TC + kWC - 1) / kWC, ctas, base + i + 1 < n ? 70 : 90);
+      p.per = aligned_share(p.KT, (p.TC + kWC - 1) / kWC, ctas, 70);
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
     // It only sets up and prefetches weights until its x warps pass griddepcontrol.wait.

@@ -225,7 +225,7 @@ def main():
   peak, peak_kind = peaks()
   # DRAM read + write bytes of one 24-matmul launch, from the ncu capture summarised in profiles/bench_launch_list.md;
   # it belongs to the full sweep only
-  traffic = 1_323_820_288 if len(work) == 24 and world == 1 else None
+  traffic = 1_315_175_744 if len(work) == 24 and world == 1 else None
   table, total_t = [], 0.0
   for c, ts in zip(work, per):
     t = statistics.median(ts)
