@@ -223,7 +223,7 @@ def main():
       _lib.call("bt_event_elapsed_ms", dev, a, b, ctypes.byref(t))
       per[i].append(t.value)
   peak, peak_kind = peaks()
-  # DRAM read + write bytes of one 24-matmul launch, from the ncu capture summarised in profiles/bench_launch_list.md;
+  # DRAM read + write bytes of one 24-matmul launch, from an ncu capture of this command (its launch list is summarised under profiles/);
   # it belongs to the full sweep only
   traffic = 1_315_175_744 if len(work) == 24 and world == 1 else None
   table, total_t = [], 0.0
