@@ -57,7 +57,6 @@ SIGNATURES = {
   "bt_gemv_check": [i32, u64, u64, ctypes.POINTER(i32)],
   "bt_gemv_queue": [i32, i32, ctypes.POINTER(GemvOp), u64, size_t, u64],
   "bt_gemv_queue_plan": [i32, ctypes.POINTER(GemvOp), ctypes.POINTER(i32)],
-  "bt_gemv_trace": [u64],
   "bt_launch_count": [ctypes.POINTER(u64)],
 }
 

@@ -9,6 +9,7 @@
 namespace bt {
 thread_local char g_error[512] = "";
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_calls{0};
 }  // namespace bt
 
 using namespace bt;

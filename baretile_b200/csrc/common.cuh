@@ -12,6 +12,7 @@ namespace bt {
 
 extern thread_local char g_error[512];
 extern std::atomic<uint64_t> g_launches;
+extern std::atomic<uint64_t> g_calls;   // entry-point calls that selected a device: a cheap "has anything else been queued since" stamp
 
 inline int fail(int code, const char *fmt, ...) {
   va_list ap;
@@ -44,6 +45,7 @@ inline int use_device(int device) {
   BT_CUDA(cudaGetDeviceCount(&n));
   if (device < 0 || device >= n) return fail(BT_BAD_ARGUMENT, "device %d: there are %d CUDA devices", device, n);
   BT_CUDA(cudaSetDevice(device));
+  g_calls.fetch_add(1, std::memory_order_relaxed);
   return BT_OK;
 }
 

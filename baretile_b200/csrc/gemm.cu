@@ -67,7 +67,11 @@ __device__ __forceinline__ uint32_t bf16_half_up(float v) { return (__float_as_u
 
 // Expand one packed tile (streaming layout, shared address `tile`) to bf16 and store it as rows [32 c, 32 c + 32) and
 // K columns [32 j, 32 j + 32) of the B tile at shared address `b` (K-major, 128-byte rows, 128-byte swizzle: the
-// 16-byte chunk index of a row is XORed with the row's index modulo 8).
+// 16-byte chunk index of a row is XORed with the row's index modulo 8). Weights are stored in offset binary: a byte
+// (or a masked nibble) zero-extended into a 16-bit lane is the bf16 number code * 2^-133, and one packed fused
+// multiply-add with the face row's power of two, minus the offset times it, makes it the exact signed weight
+// times 2^(e - 197). A nibble q is worth 16 q: a high nibble stays where it is in its byte (16 * code), a low nibble
+// takes 16 times the scale.
 template <int FMT>
 __device__ __forceinline__ void expand_tile(uint32_t tile, uint32_t b, int c, int j, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -82,16 +86,19 @@ __device__ __forceinline__ void expand_tile(uint32_t tile, uint32_t b, int c, in
     for (int fs = 0; fs < 2; fs++) {
       const uint32_t ew = ee[2 * h + fs];
       const uint32_t s01 = scale_pair<0>(ew), s23 = scale_pair<1>(ew);
-      uint32_t m0, s0, m1, s1;   // magnitude and sign bytes of channels 2g and 2g + 1, four consecutive k each
+      uint32_t a0, a1, a2, a3;   // channels 2g (a0, a2) and 2g + 1 (a1, a3), four consecutive k each
       if (FMT == BT_BFP8) {
         const uint32_t w0 = fs ? wv[h].z : wv[h].x, w1 = fs ? wv[h].w : wv[h].y;
-        m0 = w0 & 0x7F7F7F7Fu, s0 = w0 & 0x80808080u, m1 = w1 & 0x7F7F7F7Fu, s1 = w1 & 0x80808080u;
+        const uint32_t n01 = mul_bf16x2(s01, 0x80808080u), n23 = mul_bf16x2(s23, 0x80808080u);   // -128 * 2^-133 * scale
+        a0 = fma_bf16x2(w0 & 0x00FF00FFu, s01, n01), a1 = fma_bf16x2(w1 & 0x00FF00FFu, s01, n01);
+        a2 = fma_bf16x2(prmt(w0, 0u, 0x4341u), s23, n23), a3 = fma_bf16x2(prmt(w1, 0u, 0x4341u), s23, n23);
       } else {
-        const uint32_t wb = h ? (fs ? wv[0].w : wv[0].z) : (fs ? wv[0].y : wv[0].x), wl = wb << 4;
-        m0 = wl & 0x70707070u, s0 = wl & 0x80808080u, m1 = wb & 0x70707070u, s1 = wb & 0x80808080u;
+        const uint32_t wb = h ? (fs ? wv[0].w : wv[0].z) : (fs ? wv[0].y : wv[0].x), wo = prmt(wb, 0u, 0x4341u);
+        const uint32_t t01 = mul_bf16x2(s01, 0x41804180u), t23 = mul_bf16x2(s23, 0x41804180u);   // 16 * scale: a nibble q is worth 16 q
+        const uint32_t n01 = mul_bf16x2(t01, 0x80088008u), n23 = mul_bf16x2(t23, 0x80088008u);   // -8 * 2^-133 * 16 * scale
+        a0 = fma_bf16x2(wb & 0x000F000Fu, t01, n01), a1 = fma_bf16x2(wb & 0x00F000F0u, s01, n01);
+        a2 = fma_bf16x2(wo & 0x000F000Fu, t23, n23), a3 = fma_bf16x2(wo & 0x00F000F0u, s23, n23);
       }
-      const uint32_t a0 = mul_bf16x2(prmt(m0, s0, 0x5140u), s01), a1 = mul_bf16x2(prmt(m1, s1, 0x5140u), s01);
-      const uint32_t a2 = mul_bf16x2(prmt(m0, s0, 0x7362u), s23), a3 = mul_bf16x2(prmt(m1, s1, 0x7362u), s23);
       const int n0 = 32 * c + 16 * fs + 2 * g;                       // even, so n0 and n0 + 1 share an 8-row group
       const int chunk = 4 * j + 2 * h + (t >> 1);                    // 16-byte chunk of k = 32 j + 16 h + 4 t
       const uint32_t group = b + (n0 >> 3) * 1024 + (t & 1) * 8;

@@ -30,13 +30,14 @@
 // other tile row of the stage (the two halves are added through shared memory when the sub-panel ends), for a
 // gate/up pair ck picks the matrix (the up half is handed to the gate warp for the epilogue). A weight tile is
 // four 16x16 faces; a face is one m16n8k16 MMA with the face's 16 output channels as the MMA's rows, 16 input
-// channels as its K and up to 8 tokens as its columns. The 16 weights of a face row share an exponent e: the lane
-// builds bf16 lanes (sign << 15 | magnitude), i.e. +-q * 2^-133 as a bf16 subnormal, and multiplies by 2^(e - 64)
-// as a packed bf16 multiply, which gives q * 2^(e - 133) * 2^-64 exactly; the epilogue multiplies the sums by 2^64.
+// channels as its K and up to 8 tokens as its columns. The 16 weights of a face row share an exponent e; how the
+// packed bytes become exact bf16 weights times 2^(e - 197) is described at tile_mma; the epilogue multiplies the
+// sums by 2^64.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "stream_layout.cuh"
 #include <cstring>
+#include <mutex>
 
 using namespace bt;
 
@@ -110,7 +111,6 @@ struct GemvParams {
   void *out;
   float *arg_val;
   int *arg_idx;
-  unsigned long long *trace;  // when set: 8 timestamps per CTA (debugging aid)
   float alpha;
   int arg_base, M, KT, TC, epi, out_fp32;
   int fmt, pair, tg;
@@ -138,20 +138,6 @@ struct Queue {
   GemvParams op[kQueueMax];
 };
 
-#ifdef BT_GEMV_TRACE
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define BT_TRACE(slot, cond) do { if (p.trace && (cond)) p.trace[blockIdx.x * 8 + (slot)] = global_ns(); } while (0)
-// CTA 0 also stamps its first 64 stages of a matmul: stage wait over / copies issued (producer), data there /
-// stage consumed (consumer thread 0), at 2400 + 4 * stage + which
-#define BT_STAGE_TRACE(which, stage, cond) do { if (p.trace && blockIdx.x == 0 && (stage) < 32 && (cond)) p.trace[2400 + 8 * (stage) + (which)] = clock64(); } while (0)
-#else
-#define BT_TRACE(slot, cond) do { } while (0)
-#define BT_STAGE_TRACE(which, stage, cond) do { } while (0)
-#endif
 
 // Where range b of `ctas` starts: equal shares, or with `per` > 0 shares of exactly `per` units (the last one shorter).
 __host__ __device__ __forceinline__ long long range_start(long long units, int b, int ctas, int per) {
@@ -166,9 +152,26 @@ __device__ __forceinline__ int cta_of(long long u, long long units, int ctas, in
   return b;
 }
 
-// One weight tile times the staged x tile, added into acc[ng][tg][4]. `tile`, `ex` and `xs` are shared-memory
-// addresses that already include the lane's own offsets: tile = tile base + 16 * lane; ex = tile base + 16 * t,
-// where the lane's exponents are; xs = x tile base + 32 * g + 8 * t (g = lane / 4, t = lane % 4).
+// One weight tile times the staged x tile. `tile`, `ex` and `xs` are shared-memory addresses that already include
+// the lane's own offsets: tile = tile base + 16 * lane; ex = tile base + 16 * t, where the lane's exponents are;
+// xs = x tile base + 32 * g + 8 * t (g = lane / 4, t = lane % 4).
+//
+// A weight byte (offset binary, see stream_layout.cuh) zero-extended into a 16-bit lane is the bf16 number
+// byte * 2^-133, so a mask (bytes 0 and 2 of a word: the lane's first k pair) or a byte-permute (bytes 1 and 3: its
+// second pair) makes a register of two weights, and one packed fused multiply-add with the face row's power of two
+// s = 2^(e - 64) and with -offset * 2^-133 * s turns it into the exact signed weights times 2^(e - 197); the
+// epilogue multiplies the sums by 2^64. An all-zero run has e = 0: both products underflow to zero, as they should.
+//
+// bfp8: a face (16 k x 16 n) is one MMA, rows g and g + 8 of it the channels 2g and 2g + 1; acc[fs][tg] collects
+// face column fs. bfp4: a byte holds two channels of the same k, low and high nibble. The whole byte as a weight,
+// 16 * high + low, goes into one MMA ("both", acc[0]), the masked low nibble into another ("low", acc[1]); rows g of
+// these MMAs are the byte of channels (2g, 2g + 1) of face column 0, rows g + 8 that of face column 1. When a
+// sub-panel's sums are complete, 16 * high = both - low (settle below; a nibble q is worth 16 q). Sixteen registers of weights per tile either
+// way, for half as many loaded bytes.
+constexpr uint32_t kByteLanes = 0x00FF00FFu, kNibbleLanes = 0x000F000Fu, kOddBytes = 0x4341u;
+constexpr uint32_t kMinus128 = 0x80808080u;   // two bf16 lanes of -128 * 2^-133 = -2^-126
+constexpr uint32_t kMinus136 = 0x80888088u;   // -(128 + 8) * 2^-133: offset of a byte made of two offset nibbles
+constexpr uint32_t kMinus8 = 0x80088008u;     // -8 * 2^-133
 template <int FMT, int TG>
 __device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t ex, uint32_t xs, float (&acc)[2][TG][4]) {
   const uint4 ev = lds128(ex);
@@ -182,24 +185,57 @@ __device__ __forceinline__ void tile_mma(uint32_t tile, uint32_t ex, uint32_t xs
   uint4 wv[2];
   if (FMT == BT_BFP8) wv[0] = lds128(tile + 64), wv[1] = lds128(tile + 64 + 512);
   else wv[0] = lds128(tile + 64), wv[1] = wv[0];
+  uint32_t s[4][2];   // scales of face 2h + fs, first and second k pair
+#pragma unroll
+  for (int f = 0; f < 4; f++) s[f][0] = scale_pair<0>(ee[f]), s[f][1] = scale_pair<1>(ee[f]);
 #pragma unroll
   for (int h = 0; h < 2; h++) {
+    if (FMT == BT_BFP8) {
+#pragma unroll
+      for (int fs = 0; fs < 2; fs++) {
+        const int f = 2 * h + fs;
+        const uint32_t w0 = fs ? wv[h].z : wv[h].x, w1 = fs ? wv[h].w : wv[h].y;   // channels 2g and 2g + 1
+        const uint32_t n01 = mul_bf16x2(s[f][0], kMinus128), n23 = mul_bf16x2(s[f][1], kMinus128);
+        const uint32_t a0 = fma_bf16x2(w0 & kByteLanes, s[f][0], n01), a1 = fma_bf16x2(w1 & kByteLanes, s[f][0], n01);
+        const uint32_t a2 = fma_bf16x2(prmt(w0, 0u, kOddBytes), s[f][1], n23), a3 = fma_bf16x2(prmt(w1, 0u, kOddBytes), s[f][1], n23);
+#pragma unroll
+        for (int tg = 0; tg < TG; tg++) mma_bf16(acc[fs][tg], a0, a1, a2, a3, bx[h][tg].x, bx[h][tg].y);
+      }
+    } else {
+      const uint32_t w0 = h ? wv[0].z : wv[0].x, w1 = h ? wv[0].w : wv[0].y;       // face columns 0 and 1
+      const uint32_t b0 = w0 & kByteLanes, b1 = w1 & kByteLanes, b2 = prmt(w0, 0u, kOddBytes), b3 = prmt(w1, 0u, kOddBytes);
+      const uint32_t s0 = s[2 * h][0], s1 = s[2 * h + 1][0], s2 = s[2 * h][1], s3 = s[2 * h + 1][1];
+      {
+        const uint32_t a0 = fma_bf16x2(b0, s0, mul_bf16x2(s0, kMinus136)), a1 = fma_bf16x2(b1, s1, mul_bf16x2(s1, kMinus136));
+        const uint32_t a2 = fma_bf16x2(b2, s2, mul_bf16x2(s2, kMinus136)), a3 = fma_bf16x2(b3, s3, mul_bf16x2(s3, kMinus136));
+#pragma unroll
+        for (int tg = 0; tg < TG; tg++) mma_bf16(acc[0][tg], a0, a1, a2, a3, bx[h][tg].x, bx[h][tg].y);
+      }
+      {
+        const uint32_t a0 = fma_bf16x2(w0 & kNibbleLanes, s0, mul_bf16x2(s0, kMinus8)), a1 = fma_bf16x2(w1 & kNibbleLanes, s1, mul_bf16x2(s1, kMinus8));
+        const uint32_t a2 = fma_bf16x2(b2 & kNibbleLanes, s2, mul_bf16x2(s2, kMinus8)), a3 = fma_bf16x2(b3 & kNibbleLanes, s3, mul_bf16x2(s3, kMinus8));
+#pragma unroll
+        for (int tg = 0; tg < TG; tg++) mma_bf16(acc[1][tg], a0, a1, a2, a3, bx[h][tg].x, bx[h][tg].y);
+      }
+    }
+  }
+}
+
+// bfp4: from ("both", "low") sums to the arrangement the rest of the kernel uses, acc[face column][tg][j] for
+// channel 2g and [2 + j] for channel 2g + 1. "both" and "low" hold face column 0 in [0], [1] and face column 1 in
+// [2], [3]. Linear, so it may run on partial sums.
+template <int FMT, int TG>
+__device__ __forceinline__ void settle(float (&acc)[2][TG][4]) {
+  if (FMT != BT_BFP4) return;
+#pragma unroll
+  for (int tg = 0; tg < TG; tg++) {
+    float both[4], low[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) both[i] = acc[0][tg][i], low[i] = acc[1][tg][i];
 #pragma unroll
     for (int fs = 0; fs < 2; fs++) {
-      const uint32_t ew = ee[2 * h + fs];
-      const uint32_t s01 = scale_pair<0>(ew), s23 = scale_pair<1>(ew);
-      uint32_t m0, s0, m1, s1;  // magnitude and sign bytes of MMA rows g (channel 2g) and g + 8 (channel 2g + 1)
-      if (FMT == BT_BFP8) {
-        const uint32_t w0 = fs ? wv[h].z : wv[h].x, w1 = fs ? wv[h].w : wv[h].y;
-        m0 = w0 & 0x7F7F7F7Fu, s0 = w0 & 0x80808080u, m1 = w1 & 0x7F7F7F7Fu, s1 = w1 & 0x80808080u;
-      } else {
-        const uint32_t wb = h ? (fs ? wv[0].w : wv[0].z) : (fs ? wv[0].y : wv[0].x), wl = wb << 4;
-        m0 = wl & 0x70707070u, s0 = wl & 0x80808080u, m1 = wb & 0x70707070u, s1 = wb & 0x80808080u;
-      }
-      const uint32_t a0 = mul_bf16x2(prmt(m0, s0, 0x5140u), s01), a1 = mul_bf16x2(prmt(m1, s1, 0x5140u), s01);
-      const uint32_t a2 = mul_bf16x2(prmt(m0, s0, 0x7362u), s23), a3 = mul_bf16x2(prmt(m1, s1, 0x7362u), s23);
 #pragma unroll
-      for (int tg = 0; tg < TG; tg++) mma_bf16(acc[fs][tg], a0, a1, a2, a3, bx[h][tg].x, bx[h][tg].y);
+      for (int j = 0; j < 2; j++) acc[fs][tg][j] = 16.f * low[2 * fs + j], acc[fs][tg][2 + j] = both[2 * fs + j] - low[2 * fs + j];
     }
   }
 }
@@ -392,11 +428,9 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
       if (WEIGHTS) {
         const int width = min(kWC, p.TC - sp * kWC);
         const uint32_t bytes = n * width * g.tb;
-        BT_STAGE_TRACE(0, stage_no, lane == 0);
         if (lane == 0) mbar_expect_tx(full0 + 8 * b, nw * bytes);
         __syncwarp();
         if (lane < nw) bulk_g2s(stage + lane * g.matrix, w + ((size_t)sp * kWC * KT + (size_t)kt * width) * g.tb, bytes, full0 + 8 * b);
-        BT_STAGE_TRACE(1, stage_no, lane == 0);
       } else {
         if (gate) {
           // x may be the result of the launch before this one, or of an earlier matmul of this one: the host has
@@ -413,10 +447,11 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
             }
           }
           if (!__shfl_sync(0xFFFFFFFFu, ok, 0) && lane == 0) atomicExch(q.error, 5);
+          // x was written with ordinary stores (by other CTAs of this launch, or by the launch before) and is about to
+          // be read by bulk copies: order what the acquire made visible before the asynchronous proxy's reads
+          fence_proxy_async();
           gate = false;
-          BT_TRACE(1, lane == 0);
         }
-        BT_STAGE_TRACE(4, stage_no, lane == 0);
         if (p.tg == 4) {
           if (lane == 0) {
             mbar_expect_tx(full0 + 8 * b, n * 2048);
@@ -428,8 +463,6 @@ __device__ __forceinline__ void produce(const Queue &q, uint8_t *smem, uint32_t 
           __syncwarp();
           if (lane < n) bulk_g2s(stage + g.w_bytes + lane * 1024, p.x + (size_t)(kt + lane) * 2048, 1024, full0 + 8 * b);
         }
-        BT_STAGE_TRACE(5, stage_no, lane == 0);
-        BT_STAGE_TRACE(6, stage_no, lane == 0);
       }
       used += need, count++;
     }
@@ -452,14 +485,6 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
   // The ranges go round the CTAs from matmul to matmul: the CTAs that finish shared sub-panels have more to do than
   // the others, and it should not be the same ones every time.
   const int me = (cta + p.turn) % ctas;
-  BT_TRACE(0, threadIdx.x == 0);
-#ifdef BT_GEMV_TRACE
-  if (p.trace && threadIdx.x == 0) {
-    unsigned sm;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-    p.trace[blockIdx.x * 8 + 5] = sm + 1;
-  }
-#endif
   if (me >= active) return;
   Walk walk;
   walk.start(segments_of(range_start(units, me, active, p.per), range_start(units, me + 1, active, p.per), KT), KT, G.ups);
@@ -484,14 +509,11 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
   auto stage_begin = [&]() {
     slot = ring.place(G.stage);
     if (!mbar_wait(full0 + ring.bar, ring.parity, kSpinLimit)) atomicExch(q.error, 2);
-    BT_STAGE_TRACE(2, stage_no, threadIdx.x == 0);
-    BT_TRACE(2, threadIdx.x == 0 && first_stage);
     first_stage = false;
   };
   auto stage_end = [&]() {
     __syncwarp();
     mbar_arrive_if(empty0 + ring.bar, lane == 0);
-    BT_STAGE_TRACE(3, stage_no, threadIdx.x == 0);
     ring.advance();
     stage_no++;
   };
@@ -530,9 +552,9 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
         }
         stage_end();
       }
-      BT_TRACE(3, threadIdx.x == 0 && last_stage);
 
       // ---- this CTA is done with sub-panel done_sp: add the k halves, combine with other CTAs, run the epilogue ----
+      settle<FMT, TG>(acc);
       if (!PAIR) {
         // eight accumulators per lane at a time go through the 4 KiB buffer
 #pragma unroll
@@ -549,7 +571,6 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
           }
         }
       }
-      BT_TRACE(6, threadIdx.x == 0 && last_stage);
       const int first = cta_of((long long)done_sp * KT, units, active, p.per), last = cta_of((long long)(done_sp + 1) * KT - 1, units, active, p.per);
       const bool finish = me == last;         // the owner finishes the sub-panel; the others only contribute
       if (first != last) {
@@ -601,7 +622,6 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
           }
         }
       }
-      BT_TRACE(7, threadIdx.x == 0 && last_stage);
       if (finish) {
         if (PAIR) {
           // the up warp hands its sums to the gate warp of the same column
@@ -659,7 +679,6 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
     }
   }
 #undef ACC_OF
-  BT_TRACE(4, threadIdx.x == 0);
 }
 
 __global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid_constant__ Queue q) {
@@ -718,9 +737,6 @@ __global__ void __launch_bounds__(kThreads, kOcc) gemv_queue_kernel(const __grid
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------------
-
-unsigned long long *g_trace = nullptr;
-constexpr size_t kTraceStride = 4096;       // timestamps (8 bytes each) between two matmuls' records in a trace buffer
 
 int check_op(const char *who, int index, const bt_gemv_op &o) {
   BT_REQUIRE(o.fmt == BT_BFP8 || o.fmt == BT_BFP4, "%s: matmul %d: weights must be bfp8 (8) or bfp4 (4), not %d", who, index, o.fmt);
@@ -794,6 +810,24 @@ int aligned_share(int KT, int subpanels, int ctas, int least_busy_percent) {
   return 0;
 }
 
+// Whether the last thing this library queued, on any stream, before the current entry-point call was a matmul launch
+// on `stream`; and the note that one is being queued now. Entry points stamp g_calls when they select their device.
+bool follows_matmul(uint64_t stream) {
+  static std::mutex lock;
+  static struct { uint64_t stream, stamp; } last[64] = {};
+  std::lock_guard<std::mutex> hold(lock);
+  const uint64_t now = g_calls.load(std::memory_order_relaxed);
+  int slot = -1, spare = 0;
+  for (int i = 0; i < 64; i++) {
+    if (last[i].stamp && last[i].stream == stream) slot = i;
+    if (last[i].stamp < last[spare].stamp) spare = i;
+  }
+  const bool yes = slot >= 0 && last[slot].stamp + 1 == now;
+  if (slot < 0) slot = spare;
+  last[slot].stream = stream, last[slot].stamp = now;
+  return yes;
+}
+
 // Argument checks and the launches shared by the entry points. `scratch` carries the scratch pointers.
 int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Queue &scratch, uint64_t stream) {
   BT_REQUIRE(n >= 1 && ops, "%s: needs at least one matmul", who);
@@ -820,7 +854,6 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       GemvParams &p = q.op[i];
       p.x = as_ptr<uint8_t>(o.x), p.w[0] = as_ptr<uint8_t>(o.w), p.w[1] = as_ptr<uint8_t>(o.w2), p.add = as_ptr<uint16_t>(o.add);
       p.out = as_ptr<void>(o.out), p.arg_val = as_ptr<float>(o.arg_val), p.arg_idx = as_ptr<int>(o.arg_idx);
-      p.trace = g_trace ? g_trace + (size_t)(base + i) * kTraceStride : nullptr;
       p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32;
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
       p.wait_for = wait_for(ops + base, i, scratch.sets);
@@ -828,13 +861,16 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       p.per = aligned_share(p.KT, (p.TC + kWC - 1) / kWC, ctas, 70);
     }
     // Programmatic dependent launch: this grid may begin while the previous launch of the stream is still finishing.
-    // It only sets up and prefetches weights until its x warps pass griddepcontrol.wait.
+    // It only sets up and prefetches weights until its x warps pass griddepcontrol.wait. Weights read that early must
+    // be in place, so the launch overlaps its predecessor only when that was a matmul launch of this file too (which
+    // never writes weights): anything else this library queued in between (a cast, a relayout, a copy, a memset)
+    // turns the overlap off for the next matmul launch.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = kSmemBytes, cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr, cfg.numAttrs = 1;
+    cfg.attrs = attr, cfg.numAttrs = base > 0 || follows_matmul(stream) ? 1 : 0;
     BT_CUDA(cudaLaunchKernelEx(&cfg, gemv_queue_kernel, q));
     if (int st = launched("gemv_queue_kernel")) return st;
   }
@@ -938,8 +974,9 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   unsigned char *base = nullptr;
   if (int s = static_scratch(device, &base)) return s;
   if (int s = use_device(device)) return s;
-  // the array keeps whatever the last call left: flags and arrival counters must start at zero
-  BT_CUDA(cudaMemsetAsync(base, 0, kStControlBytes, as_stream(stream)));
+  // the array keeps whatever the last call left: the arrival counters must start at zero. The wait-gave-up word at
+  // its start is left alone, so that it stays until bt_gemv_check(device, 0, ...) reads it.
+  BT_CUDA(cudaMemsetAsync(base + kWsOpsDone, 0, kStControlBytes - kWsOpsDone, as_stream(stream)));
   Queue scratch{};
   scratch.error = reinterpret_cast<int *>(base + kWsError), scratch.ops_done = reinterpret_cast<int *>(base + kWsOpsDone);
   scratch.sets = 1;
@@ -950,24 +987,27 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   return enqueue("bt_gemv_bfp_static", device, 1, &op, scratch, stream);
 }
 
-// Debugging aid: when `buffer` is nonzero, every later matmul writes nanosecond timestamps, 8 per CTA, into it:
-// [0] the consumers reach the matmul, [1] the x warp may copy x, [2] first stage there, [3] last stage consumed,
-// [4] done, [5] SM number + 1, [6] k halves added, [7] partial sums combined; CTA 0 adds cycle counts for its
-// first 32 stages from 8 * 2400 bytes on. Matmul i of a queue writes at buffer + i * 32 KiB. 0 turns it off. Only
-// the trace build (-DBT_GEMV_TRACE) records.
-int bt_gemv_trace(uint64_t buffer) {
-  g_trace = as_ptr<unsigned long long>(buffer);
-  return BT_OK;
-}
-
 // Nonzero once a bounded wait inside a launch that used this scratch gave up; the results of that launch are
-// then unreliable. Reads the flag back (synchronising the stream) and clears it.
+// then unreliable. Reads the flag back (synchronising the stream) and, if it was set, clears it together with the
+// counters a launch that gave up may have left half-counted, so that the next launch starts clean. `work` = 0 means
+// the built-in scratch of bt_gemv_bfp_static on `device`.
 int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error) {
-  BT_REQUIRE(work && error, "bt_gemv_check: null argument");
+  BT_REQUIRE(error, "bt_gemv_check: null result");
+  unsigned char *base = as_ptr<unsigned char>(work);
+  if (!work) {
+    if (int s = static_scratch(device, &base)) return s;
+  }
   if (int s = use_device(device)) return s;
-  BT_CUDA(cudaMemcpyAsync(error, as_ptr<void>(work + kWsError), 4, cudaMemcpyDeviceToHost, as_stream(stream)));
+  BT_CUDA(cudaMemcpyAsync(error, base + kWsError, 4, cudaMemcpyDeviceToHost, as_stream(stream)));
   BT_CUDA(cudaStreamSynchronize(as_stream(stream)));
-  if (*error) BT_CUDA(cudaMemsetAsync(as_ptr<void>(work + kWsError), 0, 4, as_stream(stream)));
+  if (*error) {
+    if (!work) BT_CUDA(cudaMemsetAsync(base, 0, kStControlBytes, as_stream(stream)));
+    else {
+      BT_CUDA(cudaMemsetAsync(base, 0, kWsSets, as_stream(stream)));
+      for (int s = 0; s < kSets; s++)
+        BT_CUDA(cudaMemsetAsync(base + kWsSets + s * kSetBytes, 0, kSetCounters + 4 * (size_t)kMaxSubPanels, as_stream(stream)));
+    }
+  }
   return BT_OK;
 }
 

@@ -143,32 +143,40 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict
 }
 
 // ---- canonical <-> streaming layout ---------------------------------------------------------------------------
-// One block moves one tile through shared memory. To the stream: read the canonical tile in 16-byte pieces,
-// scatter its bytes to their streamed positions, write the streamed tile in 16-byte pieces. Back: the reverse.
+// A block moves one tile row of one run at a time (up to kPanel tiles, contiguous in both layouts) through shared
+// memory: 16-byte pieces in, 16-byte pieces out, each output piece gathered byte by byte through a table of the
+// permutation built once per block, value bytes recoded on the way (stream_layout.cuh). Blocks stride over the
+// matrix, so the table is built once per block and the grid is sized to the GPU.
 template <int FMT, bool TO_STREAM>
-__global__ void relayout_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
+__global__ void __launch_bounds__(256) relayout_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
   constexpr int TB = tile_bytes(FMT), PIECES = TB / 16;
-  __shared__ __align__(16) uint8_t tile[TB];
-  int ti = blockIdx.x / tc, tj = blockIdx.x % tc;
-  size_t canonical = ((size_t)ti * tc + tj) * TB, streamed = stream_tile_index(ti, tj, tr, tc) * (size_t)TB;
-  int p = threadIdx.x;
-  if (TO_STREAM) {
-    if (p < PIECES) {
-      uint4 v = *reinterpret_cast<const uint4 *>(src + canonical + p * 16);
-      uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int k = 0; k < 16; k++) tile[stream_pos<FMT>(p * 16 + k)] = (uint8_t)(w[k / 4] >> (8 * (k % 4)));
-    }
+  __shared__ uint16_t from[TB];                        // from[output byte of a tile] = input byte of the tile
+  __shared__ __align__(16) uint8_t buf[kPanel * TB];
+  for (int c = threadIdx.x; c < TB; c += blockDim.x) {
+    if (TO_STREAM) from[stream_pos<FMT>(c)] = (uint16_t)c;
+    else from[c] = (uint16_t)stream_pos<FMT>(c);
+  }
+  const int runs = (tc + kPanel - 1) / kPanel;
+  const long long groups = (long long)tr * runs;
+  for (long long gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+    const int ti = (int)(gi / runs), run = (int)(gi % runs), tj = run * kPanel, width = min(kPanel, tc - tj);
+    const size_t canonical = ((size_t)ti * tc + tj) * TB, streamed = stream_tile_index(ti, tj, tr, tc) * (size_t)TB;
+    const uint8_t *in = src + (TO_STREAM ? canonical : streamed);
+    uint8_t *out = dst + (TO_STREAM ? streamed : canonical);
+    __syncthreads();                                   // the table is ready; the previous group's reads of buf are over
+    for (int p = threadIdx.x; p < width * PIECES; p += blockDim.x)
+      *reinterpret_cast<uint4 *>(buf + p * 16) = *reinterpret_cast<const uint4 *>(in + (size_t)p * 16);
     __syncthreads();
-    if (p < PIECES) *reinterpret_cast<uint4 *>(dst + streamed + p * 16) = *reinterpret_cast<const uint4 *>(tile + p * 16);
-  } else {
-    if (p < PIECES) *reinterpret_cast<uint4 *>(tile + p * 16) = *reinterpret_cast<const uint4 *>(src + streamed + p * 16);
-    __syncthreads();
-    if (p < PIECES) {
+    for (int p = threadIdx.x; p < width * PIECES; p += blockDim.x) {
+      const int tile = p / PIECES, first = p % PIECES * 16;
       uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-      for (int k = 0; k < 16; k++) w[k / 4] |= (uint32_t)tile[stream_pos<FMT>(p * 16 + k)] << (8 * (k % 4));
-      *reinterpret_cast<uint4 *>(dst + canonical + p * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int k = 0; k < 16; k++) {
+        uint32_t b = buf[tile * TB + from[first + k]];
+        if (first >= 64) b = TO_STREAM ? stream_code<FMT>(b) : canonical_code<FMT>(b);   // a piece is all exponents or all values
+        w[k / 4] |= b << (8 * (k % 4));
+      }
+      *reinterpret_cast<uint4 *>(out + (size_t)p * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -241,14 +249,17 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
   BT_REQUIRE((long long)tile_rows * tile_cols < (1ll << 31), "bt_relayout: too many tiles for one launch");
   BT_REQUIRE(src && dst && src != dst && src % 16 == 0 && dst % 16 == 0, "bt_relayout: needs distinct 16-byte aligned buffers");
   if (int s = use_device(device)) return s;
-  unsigned blocks = (unsigned)(tile_rows * tile_cols);
+  int sms = 0;
+  BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const long long groups = (long long)tile_rows * ((tile_cols + kPanel - 1) / kPanel);
+  const unsigned blocks = (unsigned)min(groups, (long long)sms * 8);
   cudaStream_t st = as_stream(stream);
   const uint8_t *s8 = as_ptr<uint8_t>(src);
   uint8_t *d8 = as_ptr<uint8_t>(dst);
-  if (fmt == BT_BFP8 && to_stream) relayout_kernel<BT_BFP8, true><<<blocks, 96, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  else if (fmt == BT_BFP8) relayout_kernel<BT_BFP8, false><<<blocks, 96, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  else if (to_stream) relayout_kernel<BT_BFP4, true><<<blocks, 64, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  else relayout_kernel<BT_BFP4, false><<<blocks, 64, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  if (fmt == BT_BFP8 && to_stream) relayout_kernel<BT_BFP8, true><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else if (fmt == BT_BFP8) relayout_kernel<BT_BFP8, false><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else if (to_stream) relayout_kernel<BT_BFP4, true><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else relayout_kernel<BT_BFP4, false><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
   return launched("relayout_kernel");
 }
 

@@ -3,21 +3,31 @@
 // A matrix of tr x tc tiles is stored as runs of kPanel tile columns. Inside a run the tiles go tile row by
 // tile row, the run's tiles of one tile row side by side, so the tiles a CTA needs for consecutive K are one
 // contiguous range. Inside a tile the 64 exponent bytes still come first, then the values, but both are
-// permuted so that each lane of a warp fetches exactly the bytes of its MMA fragment with 128-bit loads:
+// permuted so that each lane of a warp fetches exactly the bytes of its MMA fragment with 128-bit loads, and the
+// values are recoded, one to one, from sign and magnitude to offset binary:
 //
 //   exponents  position t*16 + face*4 + j             holds the exponent of datum row k = 4t + kk of face `face`,
-//              j = 0, 1, 2, 3 for kk = 0, 2, 1, 3: a lane's word then has the exponents of its first k pair in bytes
+//              j = 0, 2, 1, 3 for kk = 0, 1, 2, 3: a lane's word then has the exponents of its first k pair in bytes
 //              0 and 2 and of its second pair in bytes 1 and 3, so one mask and one multiply-add turn each pair
 //              into two bf16 scale lanes (scale_pair below)
-//   bfp8       position 64 + h*512 + lane*16 + fs*8 + ns*4 + kk
-//              holds datum (k = 16h + 4t + kk, n = 16fs + 2g + ns), lane = 4g + t
-//   bfp4       position 64 + lane*16 + h*8 + fs*4 + kk
-//              holds the byte with datums (k = 16h + 4t + kk, n = 16fs + 2g) low nibble, (.., n + 1) high
+//   bfp8       position 64 + h*512 + lane*16 + fs*8 + ns*4 + j
+//              holds datum (k = 16h + 4t + kk, n = 16fs + 2g + ns), lane = 4g + t, as the byte 128 + v, where v
+//              is the datum's signed 7-bit integer (the byte 0x80, "minus zero", which the packer never writes,
+//              becomes 0 so that the recoding is one to one)
+//   bfp4       position 64 + lane*16 + h*8 + fs*4 + j
+//              holds the byte with datums (k = 16h + 4t + kk, n = 16fs + 2g) in its low nibble and (.., n + 1) in
+//              its high nibble, each as 8 + v (the nibble 8 becomes 0)
 //
-// with face = 2h + fs, k the row (input channel) and n the column (output channel) inside the tile. It is a
-// pure permutation of bytes: no byte is changed, duplicated or padded.
+// with face = 2h + fs, k the row (input channel) and n the column (output channel) inside the tile, and j the
+// byte of the lane's word as above. Why offset binary: a byte zero-extended into a 16-bit lane IS the bf16 number
+// byte * 2^-133 (subnormals run straight on into the first normal binade), so one mask or byte-permute per
+// register puts two weights into bf16 lanes, and one packed fused multiply-add per register, with the face row's
+// power of two and minus the offset times it, makes them the exact signed weights. Sign and magnitude would need a
+// second mask and a permute per register, on the pipe the dequantisation saturates.
+// Reading back (bt_relayout with to_stream = 0) restores every canonical byte: nothing is lost, duplicated or padded.
 #pragma once
 #include <cstddef>
+#include <cstdint>
 #include "../../include/baretile_b200.h"
 
 namespace bt {
@@ -32,11 +42,32 @@ __host__ __device__ inline int stream_pos(int c) {
   if (FMT == BT_BFP8) {
     int face = i / 256, k = i / 16 % 16, n = i % 16;
     int lane = (n / 2) * 4 + k / 4;
-    return 64 + (face / 2) * 512 + lane * 16 + (face % 2) * 8 + (n % 2) * 4 + k % 4;
+    return 64 + (face / 2) * 512 + lane * 16 + (face % 2) * 8 + (n % 2) * 4 + ((k & 1) << 1 | (k >> 1 & 1));
   }
   int face = i / 128, k = i / 8 % 16, g = i % 8;
   int lane = g * 4 + k / 4;
-  return 64 + lane * 16 + (face / 2) * 8 + (face % 2) * 4 + k % 4;
+  return 64 + lane * 16 + (face / 2) * 8 + (face % 2) * 4 + ((k & 1) << 1 | (k >> 1 & 1));
+}
+
+// Sign and magnitude (sign in the top bit of BITS bits) <-> offset binary, one to one on all 2^BITS codes.
+template <int BITS>
+__host__ __device__ inline uint32_t to_offset(uint32_t b) {
+  const uint32_t half = 1u << (BITS - 1), q = b & (half - 1);
+  return b & half ? (q ? half - q : 0u) : half + q;
+}
+template <int BITS>
+__host__ __device__ inline uint32_t from_offset(uint32_t u) {
+  const uint32_t half = 1u << (BITS - 1);
+  return u == 0 ? half : u >= half ? u - half : half | (half - u);
+}
+// A value byte (not an exponent) of a tile, canonical -> streamed coding and back.
+template <int FMT>
+__host__ __device__ inline uint32_t stream_code(uint32_t b) {
+  return FMT == BT_BFP8 ? to_offset<8>(b) : to_offset<4>(b & 15) | to_offset<4>(b >> 4) << 4;
+}
+template <int FMT>
+__host__ __device__ inline uint32_t canonical_code(uint32_t u) {
+  return FMT == BT_BFP8 ? from_offset<8>(u) : from_offset<4>(u & 15) | from_offset<4>(u >> 4) << 4;
 }
 
 #ifdef __CUDACC__

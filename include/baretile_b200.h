@@ -108,7 +108,10 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
  *   work   scratch of at least bt_gemv_workspace_bytes() bytes, zeroed once before first use;
  *          launches that share it go on one stream (where they may overlap at their edges: a launch
  *          fetches weights while the one before it finishes, and touches the scratch only after it).
- *          The weights must not be written by the launch right before it in the stream.
+ *          That overlap happens only behind another matmul launch of this library: after any other call of
+ *          this library (a cast, a relayout, a copy) the launch starts once everything before it is complete.
+ *          Work queued on the stream by other means and writing the weights needs a synchronisation of the
+ *          caller's before the matmul.
  * Products are exact, sums are fp32, outputs round half up to bf16 like the packer
  * (docs/compiler.md, "Matmul precision"). */
 int bt_gemv_workspace_bytes(int device, size_t *bytes);
@@ -158,19 +161,17 @@ int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
  * Limits, rejected with BT_BAD_ARGUMENT: M <= 8 rows of x, N <= 524288 columns. Inputs and outputs are the
  * caller's, exactly as for bt_gemv_bfp. The first call on a device looks the array's address up (one runtime
  * query); make that first call outside any stream capture. All calls on a device share the one array and each
- * call first clears the flags and counters it keeps there, so two calls whose kernels overlap on the GPU (different
- * streams) race: keep them on one stream or serialise them. */
+ * call first clears the counters it keeps there, so two calls whose kernels overlap on the GPU (different
+ * streams) race: keep them on one stream or serialise them. The word that records a wait that gave up is not cleared
+ * by a call: it stays until bt_gemv_check(device, 0, stream, &error) reads it. */
 int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, uint64_t x, uint64_t w, uint64_t w2,
                        uint64_t add, float alpha, uint64_t out, int out_dtype, uint64_t arg_val, uint64_t arg_idx,
                        int arg_base, uint64_t stream);
 /* Nonzero in *error once a bounded wait inside a launch that used this scratch gave up (its results are then
  * unreliable): the counterpart of Runtime.wait's timeout report (baretile/runtime.py:866-876). Synchronises the
- * stream, and clears the flag. */
+ * stream; if the flag was set, clears it and the counters that launch may have left half-counted. work = 0 asks
+ * about the built-in scratch of bt_gemv_bfp_static on that device. */
 int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error);
-/* Debugging aid (the reference's kernel print rings, baretile/runtime.py:882-901): with a nonzero device buffer,
- * every later matmul writes 8 nanosecond timestamps per CTA into it, matmul i of a queue at buffer + i * 32 KiB.
- * 0 turns it off. Only a library built with -DBT_GEMV_TRACE records anything. */
-int bt_gemv_trace(uint64_t buffer);
 /* Number of GPU kernels this library has launched on behalf of the calling process. */
 int bt_launch_count(uint64_t *count);
 

@@ -143,20 +143,20 @@ def unpack_tiles(tiles, dtype):
   return np.where(mag == 0, np.where(x >> 7 != 0, 0xFF80, 0), out).astype(np.uint16)
 
 
-# ---- streaming layout (the B200 backend's own `columns()` permutation) -------------------------------
+# ---- streaming layout (the B200 backend's own `columns()` layout) ---------------------------------------
 
 PANEL = 4  # tile columns per run
 
 
 def stream_perm(dtype):
   """Byte permutation inside one tile for the streaming layout: position p of the streamed tile holds
-  canonical byte stream_perm[p]. It is defined by this backend (the reference's columns() is likewise a
-  pure permutation that reads back unchanged, baretile/kernels.py:1455-1481).
+  canonical byte stream_perm[p] (recoded, see stream_code). It is defined by this backend (the reference's
+  columns() is likewise a rearrangement that reads back unchanged, baretile/kernels.py:1455-1481).
 
-  Exponents: position t*16 + face*4 + j holds the exponent of run face*16 + 4t + kk, j = 0, 1, 2, 3 for
-  kk = 0, 2, 1, 3.
-  bfp8 values: position 64 + h*512 + lane*16 + fs*8 + ns*4 + kk, with lane = g*4 + t, holds datum
-  (k = 16h + 4t + kk, n = 16fs + 2g + ns). bfp4 values: position 64 + lane*16 + h*8 + fs*4 + kk holds the
+  Exponents: position t*16 + face*4 + j holds the exponent of run face*16 + 4t + kk, j = 0, 2, 1, 3 for
+  kk = 0, 1, 2, 3.
+  bfp8 values: position 64 + h*512 + lane*16 + fs*8 + ns*4 + j, with lane = g*4 + t, holds datum
+  (k = 16h + 4t + kk, n = 16fs + 2g + ns). bfp4 values: position 64 + lane*16 + h*8 + fs*4 + j holds the
   byte with datums (k = 16h + 4t + kk, n = 16fs + 2g) and (…, n + 1)."""
   perm = np.zeros(tile_bytes(dtype), np.int64)
   for t in range(4):
@@ -168,21 +168,44 @@ def stream_perm(dtype):
         lane = g * 4 + t
         for fs in range(2):
           for kk in range(4):
-            k = 16 * h + 4 * t + kk
+            k, j = 16 * h + 4 * t + kk, (0, 2, 1, 3)[kk]
             if dtype == "bfp8":
               for ns in range(2):
-                perm[64 + h * 512 + lane * 16 + fs * 8 + ns * 4 + kk] = 64 + at(k, 16 * fs + 2 * g + ns)
+                perm[64 + h * 512 + lane * 16 + fs * 8 + ns * 4 + j] = 64 + at(k, 16 * fs + 2 * g + ns)
             else:
-              perm[64 + lane * 16 + h * 8 + fs * 4 + kk] = 64 + at(k, 16 * fs + 2 * g) // 2
+              perm[64 + lane * 16 + h * 8 + fs * 4 + j] = 64 + at(k, 16 * fs + 2 * g) // 2
   assert sorted(perm.tolist()) == list(range(tile_bytes(dtype)))
   return perm
+
+
+def _offset_tables(bits):
+  """Sign and magnitude (sign in the top bit) -> offset binary half + v, one to one: the code "minus zero",
+  which the packer never writes, takes the one spare offset code, 0."""
+  half = 1 << (bits - 1)
+  fwd = np.zeros(1 << bits, np.uint8)
+  for b in range(1 << bits):
+    q = b & (half - 1)
+    fwd[b] = (half - q if q else 0) if b & half else half + q
+  assert sorted(fwd.tolist()) == list(range(1 << bits))
+  return fwd, np.argsort(fwd).astype(np.uint8)
+
+
+def stream_code(values, dtype, back=False):
+  """Value bytes of tiles, canonical coding -> the streaming layout's offset binary (bfp8: 128 + v per byte;
+  bfp4: 8 + v per nibble), or back."""
+  v = np.asarray(values, np.uint8)
+  if dtype == "bfp8": return _offset_tables(8)[1 if back else 0][v]
+  t = _offset_tables(4)[1 if back else 0]
+  return t[v & 15] | t[v >> 4] << 4
 
 
 def to_stream(tiles, dtype, tr, tc):
   """Canonical block-float tiles of one (tr x tc)-tile matrix -> streaming layout: runs of PANEL tile
   columns; inside a run, tile row by tile row, the run's tiles of that row side by side, each tile's
-  bytes permuted by stream_perm."""
-  t = np.asarray(tiles, np.uint8).reshape(tr, tc, tile_bytes(dtype))[:, :, stream_perm(dtype)]
+  value bytes recoded by stream_code and all its bytes permuted by stream_perm."""
+  t = np.asarray(tiles, np.uint8).reshape(tr, tc, tile_bytes(dtype)).copy()
+  t[:, :, 64:] = stream_code(t[:, :, 64:], dtype)
+  t = t[:, :, stream_perm(dtype)]
   return np.concatenate([t[:, p:p + PANEL].reshape(-1) for p in range(0, tc, PANEL)])
 
 
@@ -194,6 +217,7 @@ def from_stream(data, dtype, tr, tc):
     w = min(PANEL, tc - p)
     out[:, p:p + w] = data[off:off + tr * w * tb].reshape(tr, w, tb)[:, :, inv]
     off += tr * w * tb
+  out[:, :, 64:] = stream_code(out[:, :, 64:], dtype, back=True)
   return out.reshape(tr * tc, tb)
 
 

@@ -69,11 +69,21 @@ def test_known_answers(c_oracle):
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
 def test_stream_layout_is_a_permutation(fmt):
+  # positions are permuted, value bytes recoded one to one (sign and magnitude -> offset binary), and it reads back
   rng = np.random.default_rng(2)
+  perm = o.stream_perm(fmt)
+  assert sorted(perm.tolist()) == list(range(o.tile_bytes(fmt))) and sorted(perm[:64].tolist()) == list(range(64))
+  every = np.arange(256, dtype=np.uint8)
+  coded = o.stream_code(every, fmt)
+  assert sorted(coded.tolist()) == list(range(256)) and np.array_equal(o.stream_code(coded, fmt, back=True), every)
+  if fmt == "bfp8":   # the byte is 128 + the signed magnitude; "minus zero" takes the spare code 0
+    assert [int(coded[b]) for b in (0, 1, 127, 0x81, 0xFF, 0x80)] == [128, 129, 255, 127, 1, 0]
+  else:               # each nibble is 8 + its signed magnitude
+    assert [int(coded[b]) for b in (0x00, 0x71, 0x9F, 0x88)] == [0x88, 0xF9, 0x71, 0x00]
   for tr, tc in ((1, 1), (3, 5), (2, 16), (4, 37)):
     tiles = rng.integers(0, 256, (tr * tc, o.tile_bytes(fmt)), dtype=np.uint16).astype(np.uint8)
     s = o.to_stream(tiles, fmt, tr, tc)
-    assert s.size == tiles.size and np.array_equal(np.sort(s), np.sort(tiles.reshape(-1)))
+    assert s.size == tiles.size
     assert np.array_equal(o.from_stream(s, fmt, tr, tc), tiles)
 
 
