@@ -22,11 +22,13 @@ class Bound(int):
     return self
 
 
-def _merge_holes(holes):
+def _merge_holes(holes, starts=()):
+  """Join adjacent holes, but never across the start of an arena: two arenas that happen to be neighbours in the
+  address space are separate allocations of the driver, and one copy or tensor must not span both."""
   holes.sort()
   merged = []
   for addr, room in holes:
-    if merged and merged[-1][0] + merged[-1][1] == addr: merged[-1] = (merged[-1][0], merged[-1][1] + room)
+    if merged and merged[-1][0] + merged[-1][1] == addr and addr not in starts: merged[-1] = (merged[-1][0], merged[-1][1] + room)
     else: merged.append((addr, room))
   holes[:] = merged
 
@@ -35,18 +37,22 @@ class Recording:
   """Launches recorded once and replayed with one call: the reference's Recording / tensor.jit
   (baretile/tensor.py:1171-1293), which replays a block of commands with one doorbell write. Here the block is a
   CUDA graph, and matmuls that follow one another in it become one queue launch (see Runtime.queue). Recorded
-  launches keep their addresses, so the tensors they use must stay alive.
+  launches keep their addresses, so the tensors they use must stay alive. Memory that is released while recording
+  (a temporary of a launch: staging for an upload, the flat scratch of a pick) is used by every replay, so the
+  recording keeps it out of the allocator until close().
 
       with rt.record() as step: y = (x @ w).relu().realize()
       step.replay()
   """
-  def __init__(self, rt): self.rt, self.graph, self.count = rt, None, 0
+  def __init__(self, rt): self.rt, self.graph, self.count, self.held = rt, None, 0, []
   def __enter__(self):
     self.rt.check()
+    if self.rt.recording is not None: raise RuntimeError("a recording is already in progress on this runtime")
     self.rt.flush()
     self.first = self.rt.launches
     _lib.call("bt_graph_begin", self.rt.device, self.rt.stream)
     self.outer, self.rt.pending = self.rt.pending, []
+    self.rt.recording = self
     return self
   def __exit__(self, kind, *_):
     graph = ctypes.c_uint64()
@@ -54,7 +60,7 @@ class Recording:
       try:
         if kind is None: self.rt.flush()
       finally:
-        self.rt.pending = self.outer
+        self.rt.pending, self.rt.recording = self.outer, None
         _lib.call("bt_graph_end", self.rt.device, self.rt.stream, ctypes.byref(graph))
     except Exception:
       if kind is None: raise
@@ -66,8 +72,14 @@ class Recording:
     _lib.call("bt_graph_launch", self.rt.device, self.graph, self.rt.stream)
     self.rt.launches += self.count
   def close(self):
+    """Drop the recording and hand the memory it kept back to the allocator."""
     if self.graph is not None and self.rt.active: _lib.lib().bt_graph_destroy(self.rt.device, self.graph)
     self.graph = None
+    held, self.held = self.held, []
+    for addr, size in held:
+      if self.rt.active:
+        self.rt.holes.append((addr, size))
+        _merge_holes(self.rt.holes, {a for a, _ in self.rt.arenas})
 
 
 class Queue:
@@ -105,6 +117,7 @@ class Runtime:
     self.numbers = {}                                # 1 x 1 tensors of Python numbers, made once
     self.log = None
     self.pending = None      # matmuls collected for one queue launch (a list while queueing)
+    self.recording = None    # the Recording in progress, which keeps what is freed meanwhile
     self.stream = ctypes.c_uint64()
     for other in list(chip.taken.values()): other.close()
     _lib.call("bt_stream_create", self.device, ctypes.byref(self.stream))
@@ -253,8 +266,11 @@ class Runtime:
     if not self.active: return
     size = self.used.pop(addr, None)
     if size is None: return
+    if self.recording is not None:   # a replay will use this memory again
+      self.recording.held.append((addr, size))
+      return
     self.holes.append((addr, size))
-    _merge_holes(self.holes)
+    _merge_holes(self.holes, {a for a, _ in self.arenas})
 
   def record(self): return Recording(self)
 

@@ -36,12 +36,19 @@ def raw_tiles(rt, t):
   return np.frombuffer(rt.download(t.addr, t.tiles * tb), np.uint8).reshape(t.tiles, tb)
 
 
-def check_matmul(got, x, wd, ref, tol=1e-2):
-  """The two bounds the reference uses: max relative error (docs/workload.md:141) within tol, and every element
-  within a bf16 step of sum |x||w| (test/test_kernels.py:745)."""
+def check_matmul(got, x, wd, ref, tol=1e-2, addend=None, alpha=1.0):
+  """The two bounds the reference uses: max relative error (docs/workload.md:141) within tol, and, when the
+  dequantised weights wd are given (a linear or ReLU result: a 1-Lipschitz epilogue), every element within
+  2^-8 of sum |x||w| (+ |addend|), the bound of test/test_kernels.py:745: half a bf16 step of the largest value
+  the sum could have, which covers the one rounding of the result; accumulation is fp32 over exact products."""
   got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
   assert got.shape == ref.shape, (got.shape, ref.shape)
   assert np.isfinite(got).all()
   err = o.rel_err(got, ref)
   assert err <= tol, err
+  if wd is not None and x is not None:
+    room = abs(alpha) * (np.abs(np.asarray(x, np.float64)) @ np.abs(np.asarray(wd, np.float64)))
+    if addend is not None: room = room + np.abs(np.asarray(addend, np.float64))
+    over = np.abs(got - ref) - 2.0 ** -8 * room * (1 + 2.0 ** -10) - 1e-30
+    assert (over <= 0).all(), (float(over.max()), np.unravel_index(over.argmax(), over.shape))
   return err

@@ -32,7 +32,10 @@ def run(rt, x, w, fmt, epilogue="none", w2=None, dtype=None, columns=True, add=N
   names, rt.log = [name for *_, name in rt.log], None
   # one matmul launch per tile row of x, with the epilogue fused; a B not yet by columns is first laid out, once
   assert sum(n.startswith("matmul") for n in names) == -(-x.shape[0] // 32) and len(names) <= -(-x.shape[0] // 32) + (0 if columns else 2)
-  return got.numpy(), ref
+  out = got.numpy()
+  if epilogue in ("none", "relu"):   # every element within 2^-8 of sum |x||w| (+ |addend|): the reference's per-element bound
+    check_matmul(out, x, wd, ref, TOL_BF16 if dtype != "fp32" else TOL_FP32, addend=add, alpha=alpha if alpha is not None else 1.0)
+  return out, ref
 
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
@@ -318,3 +321,121 @@ def test_unsupported_expressions_raise(rt):
   with pytest.raises(ValueError, match="fidelity"): x.matmul(w.cast("bfp8"), fidelity=5)
   with pytest.raises(ValueError): (x @ w.cast("bfp8")).topk(2)
   rt.wait()
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("m", [1, 5, 16, 32])
+def test_results_stay_inside_their_tiles(rt, fmt, m):
+  # Guard regions either side of the result (the reference's canary trick, test/test_kernels.py:665-680): the kernel
+  # writes the result's tiles and nothing else; token rows past M are zero, and a one-row result fills its tile.
+  from baretile_b200 import _lib
+  rng = np.random.default_rng(17 + m)
+  k, n = 512, 736
+  x, w = acts(rng, m, k), weights(rng, k, n)
+  tx, tw = upload(rt, x), upload(rt, w).cast(fmt).columns()
+  guard, size = 4096, (n // 32) * 2048
+  buf = rt.dram_alloc(size + 2 * guard)
+  try:
+    _lib.call("bt_memset", rt.device, buf, 0xA5, size + 2 * guard, rt.stream)
+    _lib.call("bt_gemv_bfp", rt.device, int(fmt[3]), 0, m, k, n, tx.addr, tw.addr, 0, 0, ctypes.c_float(1.0), buf + guard, 0, 0, 0, 0,
+              rt.work, rt.work_bytes, rt.stream)
+    rt.wait()
+    raw = np.frombuffer(rt.download(buf, size + 2 * guard), np.uint8)
+  finally: rt.dram_free(buf)
+  assert (raw[:guard] == 0xA5).all() and (raw[-guard:] == 0xA5).all()
+  tiles = np.frombuffer(raw[guard:-guard].tobytes(), np.uint16).reshape(-1, 1024)
+  full = o.bf16_floats(o.untilize(tiles, 1, 32, n)[0])              # all 32 rows of the tile row
+  ref = x.astype(np.float32) @ o.dequant(w, fmt)
+  check_matmul(full[:m], x, o.dequant(w, fmt), ref, TOL_BF16)
+  if m == 1: assert (full == full[0]).all()                         # a single row repeats across its tile
+  else: assert not full[m:].any()                                   # rows past M are zero
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_matmul_right_after_its_weights_were_written(rt, fmt):
+  # cast, columns() and the matmul queued back to back on a large matrix: the matmul's early weight fetches must not
+  # overtake the kernels that write the weights (the launch only overlaps a preceding matmul launch)
+  rng = np.random.default_rng(3)
+  k, n = 4096, 14336
+  x, w = acts(rng, 8, k), weights(rng, k, n)
+  tx, tb = upload(rt, x), upload(rt, w)
+  warm = (tx @ upload(rt, weights(rng, k, 512)).cast(fmt).columns()).realize()    # a matmul launch right before
+  y = (tx @ tb.cast(fmt).columns()).realize()                      # pack, relayout and matmul with nothing in between
+  rt.wait()
+  check_matmul(y.numpy(), x, o.dequant(w, fmt), x @ o.dequant(w, fmt), TOL_BF16)
+  del warm
+
+
+def _tiled(rt, block, reps_k, reps_n, fmt, scales=None):
+  """A big weight matrix made of a seeded block repeated reps_k x reps_n times (column copy i scaled by scales[i]), as a
+  Tensor in streaming layout, and the dequantised values of one row of blocks. Runs of 16 never straddle a block
+  (its width is a multiple of 16), so the block's packed values are the big matrix' packed values; only one row of
+  blocks crosses the bus, the others are copies made on the device (tile rows are contiguous in tile layout)."""
+  from baretile_b200.tensor import Tensor
+  scales = scales if scales is not None else [1.0] * reps_n
+  cols = [bf16(block * s) for s in scales]
+  row = np.concatenate(cols, axis=1)
+  wd_row = np.concatenate([o.dequant(c, fmt) for c in cols], axis=1)
+  first = upload(rt, row)
+  k, n = block.shape[0] * reps_k, row.shape[1]
+  full = Tensor(rt, k, n)
+  for r in range(reps_k): rt.launch("bt_d2d", (full.addr + r * first.tiles * 2048, first.addr, first.tiles * 2048), name="copy")
+  return full.cast(fmt).columns(), wd_row
+
+
+def _folded(x, reps_k):
+  """x @ tile(B, (reps_k, 1)) = (sum of x's reps_k column blocks) @ B: the activations folded onto one row of blocks, in float64."""
+  m, k = x.shape
+  return x.astype(np.float64).reshape(m, reps_k, k // reps_k)
+
+
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
+@pytest.mark.parametrize("m", [1, 32])
+def test_llama_shapes_other_row_counts(rt, k, n, m):
+  # configs[1] at M = 1 and M = 32 on the three full shapes (M = 8 is test_llama_shapes)
+  rng = np.random.default_rng(k + n + m)
+  x, w = acts(rng, m, k), weights(rng, k, n)
+  for fmt in ("bfp8", "bfp4"):
+    got, ref = run(rt, x, w, fmt)
+    check_matmul(got, x, None, ref, TOL_BF16)
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_llama70b_layer_shapes(rt, m):
+  # configs[3] on one GPU at full size: gate/up [8192, 28672] bfp4 fused, then down [28672, 8192] bfp4
+  rng = np.random.default_rng(70 + m)
+  bg, bu, bd = weights(rng, 1024, 1024), weights(rng, 1024, 1024), weights(rng, 1024, 1024)
+  x = acts(rng, m, 8192)
+  tx = upload(rt, x)
+  (tg, dg), (tu, du), (td, dd) = _tiled(rt, bg, 8, 28, "bfp4"), _tiled(rt, bu, 8, 28, "bfp4"), _tiled(rt, bd, 28, 8, "bfp4")
+  h = ((tx @ tg).silu() * (tx @ tu)).realize()
+  y = (h @ td).realize()
+  hg = h.numpy()
+  xf = _folded(x, 8).sum(1)
+  ref_h = o.silu((xf @ dg).astype(np.float32)) * (xf @ du).astype(np.float32)
+  check_matmul(hg, x, None, ref_h, TOL_BF16)
+  hf = _folded(hg, 28)
+  check_matmul(y.numpy(), None, None, hf.sum(1) @ dd, TOL_BF16)
+  room = np.abs(hf).sum(1) @ np.abs(dd)                             # the per-element bound, 2^-8 of sum |h||w|
+  assert (np.abs(y.numpy() - hf.sum(1) @ dd) <= 2.0 ** -8 * room * (1 + 2.0 ** -10)).all()
+
+
+@pytest.mark.parametrize("m", [1, 4, 8])
+def test_lm_head_pick_full_size(rt, m):
+  # configs[4] on one GPU: x[M, 8192] @ W[8192, 128256] bfp8 with the fused greedy pick; the index is exact against
+  # the kernel's own fp32 logits everywhere, and against the oracle outside the stated near-ties
+  rng = np.random.default_rng(400 + m)
+  block = weights(rng, 1024, 2672)                                 # 48 copies side by side make the 128256 columns
+  tw, wd = _tiled(rt, block, 8, 48, "bfp8", scales=[1 + i / 64 for i in range(48)])
+  x = acts(rng, m, 8192)
+  tx = upload(rt, x)
+  values, ids = (tx @ tw).topk(1)
+  got_ids, got_vals = np.array(ids.tolist())[:, 0], np.array(values.tolist())[:, 0]
+  full = tx.matmul(tw, dtype="fp32").realize().numpy()
+  assert np.array_equal(got_ids, o.argmax(full)) and np.array_equal(got_vals, full.max(-1))
+  xf = _folded(x, 8)
+  logits = xf.sum(1) @ wd
+  assert o.rel_err(full, logits) <= TOL_FP32
+  top2 = np.sort(logits, -1)[:, -2:]
+  near = top2[:, 1] - top2[:, 0] <= 2.0 ** -8 * (np.abs(xf).sum(1) @ np.abs(wd)).max(-1)
+  assert np.array_equal(got_ids[~near], o.argmax(logits)[~near]), ("near ties at rows", np.nonzero(near)[0].tolist())

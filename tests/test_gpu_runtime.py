@@ -57,3 +57,86 @@ def test_second_runtime_replaces_the_first():
   with pytest.raises(RuntimeError, match="closed"): Tensor.zeros(a, 1, 1)
   b.close(); b.close()
   assert b.closed
+
+
+def _chain(rt, tx, layers, head):
+  """x through gate/up pairs and down projections, each reading the one before it, then the greedy pick of a head."""
+  h = tx
+  for wg, wu, wd in layers:
+    a = ((h @ wg).silu() * (h @ wu)).realize()
+    h = (a @ wd).relu().realize()
+  values, ids = (h @ head).topk(1)
+  return h, values, ids
+
+
+def test_record_and_replay(rt):
+  # a recorded dependent chain (with a pick, whose scratch is a temporary) replays bit for bit like plain launches,
+  # also after its input changed in place and after later allocations took whatever memory was free
+  # (baretile/tensor.py:1171-1293: a Recording replays a block of commands with one doorbell write)
+  from helpers import acts, upload, weights
+  from baretile_b200.tensor import Tensor
+  rng = np.random.default_rng(101)
+  host = [(weights(rng, 512, 1024) * 2, weights(rng, 512, 1024) * 2, weights(rng, 1024, 512) * 2) for _ in range(3)]
+  layers = [tuple(upload(rt, w).cast(fmt).columns() for w in ws) for ws, fmt in zip(host, ("bfp8", "bfp4", "bfp8"))]
+  head = upload(rt, weights(rng, 512, 2016)).cast("bfp8").columns()
+  xs = [acts(rng, 4, 512) for _ in range(3)]
+  tx = upload(rt, xs[0])
+  want = []
+  for x in xs:                                                     # plain launches, one input after the other
+    h, values, ids = _chain(rt, upload(rt, x), layers, head)
+    want.append((h.numpy(), values.numpy(), ids.numpy()))
+  used_before = set(rt.used)
+  with rt.record() as step:
+    h, values, ids = _chain(rt, tx, layers, head)
+  assert step.held, "the pick's scratch was released while recording and must stay with the recording"
+  later = [Tensor.zeros(rt, 64, 512) for _ in range(8)]            # takes free memory: must not be what a replay writes
+  for x, (wh, wv, wi) in zip(xs, want):
+    staged = upload(rt, x)
+    rt.launch("bt_d2d", (tx.addr, staged.addr, tx.tiles * 2048), name="copy")   # new input, same address
+    step.replay()
+    rt.wait()
+    assert np.array_equal(h.numpy(), wh) and np.array_equal(values.numpy(), wv) and np.array_equal(ids.numpy(), wi)
+  assert all(not np.array(t.tolist()).any() for t in later[:2])    # and a replay wrote nothing into the later tensors
+  step.close()
+  del h, values, ids, later, staged
+  assert set(rt.used) - used_before <= {tx.addr}
+
+
+def test_wait_times_out_and_the_runtime_stays_usable(rt):
+  # Runtime.wait(timeout) raises TimeoutError while work is still queued (baretile/runtime.py:858-876); nothing hangs:
+  # the queued work is a few long memsets, and a later wait finds them done
+  from baretile_b200.tensor import Tensor
+  size = 2 << 30
+  big = rt.dram_alloc(size)
+  try:
+    for _ in range(6): rt.launch("bt_memset", (big, 0, size), name="zeros")
+    with pytest.raises(TimeoutError, match="did not finish"): rt.wait(timeout=0.0001)
+    rt.wait()
+    assert not np.array(Tensor.zeros(rt, 32, 32).tolist()).any()
+  finally: rt.dram_free(big)
+
+
+def test_bounded_device_wait_reports_instead_of_hanging(rt):
+  # A wait inside the matmul kernel that cannot be met gives up after its limit and sets the error word, which
+  # Runtime.wait turns into RuntimeError; the kernel ends normally and the runtime keeps working. The wait is made
+  # unmeetable on the host: the arrival counters of the matrix' sub-panels in the scratch start far below zero, so
+  # a sub-panel's owner never sees its contributors arrive. Offsets: the first scratch set starts at byte 256 of the
+  # workspace and its counters (one int per sub-panel of 4 tile columns) 256 bytes further (kWsSets, kSetCounters in
+  # csrc/gemv.cu).
+  from helpers import acts, upload, weights
+  from oracle import bfp_oracle as o
+  rng = np.random.default_rng(5)
+  x, w = acts(rng, 4, 4096), weights(rng, 4096, 512)               # 4 sub-panels, each shared by many CTAs
+  tx, tw = upload(rt, x), upload(rt, w).cast("bfp8").columns()
+  good = (tx @ tw).realize().numpy()
+  rt.wait()
+  counters = rt.work + 256 + 256
+  poisoned = (ctypes.c_int * 4)(*([-1000] * 4))
+  rt.upload(counters, bytes(poisoned))
+  y = (tx @ tw).realize()
+  with pytest.raises(RuntimeError, match="gave up on a bounded wait"): rt.wait()
+  rt.wait()                                                        # the flag was read and cleared, the counters reset
+  again = (tx @ tw).realize().numpy()
+  assert np.array_equal(again, good)
+  assert o.rel_err(good, x @ o.dequant(w, "bfp8")) <= 1e-2
+  del y

@@ -50,6 +50,35 @@ def test_static_scratch_matches_twice_in_a_row(rt):
     assert o.rel_err(got, ref) <= 1e-2, call
 
 
+def test_static_scratch_pick_and_its_error_word(rt):
+  # the greedy pick through the built-in scratch, twice, against the ordinary entry point; and the word that records a
+  # wait that gave up is readable for the built-in scratch too (work = 0) and reads zero after clean runs
+  from baretile_b200 import _lib
+  rng = np.random.default_rng(9)
+  m, k, n = 5, 1024, 4000 // 32 * 32
+  flat = rt.dram_alloc(1024)
+  try:
+    for call in range(2):
+      x, w = acts(rng, m, k), weights(rng, k, n)
+      tx, tw = upload(rt, x), upload(rt, w).cast("bfp8").columns()
+      picks = []
+      for static in (True, False):
+        _lib.call("bt_memset", rt.device, flat, 0xFF, 1024, rt.stream)
+        args = (rt.device, 8, 4, m, k, n, tx.addr, tw.addr, 0, 0, ctypes.c_float(1.0), 0, 0, flat, flat + 512, 7)
+        if static: _lib.call("bt_gemv_bfp_static", *args, rt.stream)
+        else: _lib.call("bt_gemv_bfp", *args, rt.work, rt.work_bytes, rt.stream)
+        rt.wait()
+        raw = rt.download(flat, 1024)
+        picks.append((np.frombuffer(raw[:4 * m], np.float32).copy(), np.frombuffer(raw[512:512 + 4 * m], np.int32).copy()))
+      assert np.array_equal(picks[0][0], picks[1][0]) and np.array_equal(picks[0][1], picks[1][1]), call
+      logits = tx.matmul(tw, dtype="fp32").realize().numpy()
+      assert np.array_equal(picks[0][1] - 7, o.argmax(logits)) and np.array_equal(picks[0][0], logits.max(-1))
+    error = ctypes.c_int(-1)
+    _lib.call("bt_gemv_check", rt.device, 0, rt.stream, ctypes.byref(error))
+    assert error.value == 0
+  finally: rt.dram_free(flat)
+
+
 def test_static_scratch_rejects_what_it_cannot_hold(rt):
   from baretile_b200 import _lib
   with pytest.raises(ValueError, match="up to 8 rows"):
