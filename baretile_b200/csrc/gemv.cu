@@ -794,18 +794,21 @@ int wait_for(const bt_gemv_op *ops, int i, int sets) {
 }
 
 // Units per CTA such that range boundaries fall on sub-panel boundaries (a share that divides a sub-panel's K tiles,
-// or a whole number of sub-panels), when that keeps at least the given percentage of the CTAs busy; else 0: equal
-// shares of all CTAs, whose ranges straddle sub-panels. With fitted shares a CTA has one piece per matmul instead of
-// up to three, and a sub-panel's partial sums come from fewer CTAs. Inside a queue the CTAs left without a share go
-// on to the next matmul. The choice depends on the shape only, never on a matmul's place in a queue: the way the sums
-// are grouped, and with it the last bit of a result, must not change with how matmuls are batched.
+// or a whole number of sub-panels), when that keeps enough of the CTAs busy; else 0: equal shares of all CTAs, whose
+// ranges straddle sub-panels. With fitted shares a CTA has one piece per matmul instead of up to three, and a
+// sub-panel's partial sums come from fewer CTAs. That is worth idle CTAs only while ranges are short and the hand-over
+// of partial sums weighs against the streaming: up to kShortRange units per CTA a fitted share is taken if it keeps
+// 70 % of the CTAs busy (inside a queue the CTAs left without a share go on to the next matmul), beyond that only if it
+// keeps 97 % busy. The choice depends on the shape only, never on a matmul's place in a queue: the way the sums are
+// grouped, and with it the last bit of a result, must not change with how matmuls are batched.
+constexpr int kShortRange = 96;
 int aligned_share(int KT, int subpanels, int ctas, int least_busy_percent) {
   const long long units = (long long)subpanels * KT;
   const int least = (int)((units + ctas - 1) / ctas);
   for (int d = least; d <= 4 * least && d <= units; d++) {
     if (KT % d != 0 && d % KT != 0) continue;
     const long long busy = (units + d - 1) / d;
-    return busy * 100 >= (long long)least_busy_percent * ctas ? d : 0;
+    return busy * 100 >= (long long)(least <= kShortRange ? least_busy_percent : 97) * ctas ? d : 0;
   }
   return 0;
 }
