@@ -1,6 +1,6 @@
 """Benchmark of the block-float matmul path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--reference PATH]
 
 Workload at every N (per GPU): the decode GEMV sweep on Llama-3-8B-shaped random weights: K x N in {4096x4096,
 4096x14336, 14336x4096}, bfp8 and bfp4, M in {1, 8, 32} rows of bf16 activations, plus the fused gate/up pair
@@ -14,11 +14,19 @@ graph, timed with CUDA events on the launching stream). `e2e` is the same step t
 host buffers: every matmul's activations are copied from page-locked host memory, tilized, multiplied, untilized and
 copied back inside the timed region (recorded once with Runtime.record() and replayed, then waited for). With N > 1 every rank runs the same sweep on its own GPU (weak scaling, no
 data-path collective), times are the maximum over ranks, and the sharded configurations that do exchange data are
-measured separately (see `sharded` in the output).
+measured separately (`config.sharded`).
 
---impl reference times the reference's CPU path, restated in NumPy (oracle/bfp_oracle.py), on a bounded sample.
+Beside the headline, in `config`: `chain`, a Llama-3-8B decode layer chain (o-proj 4096x4096 -> fused gate/up
+4096x14336 -> down 14336x4096, every matmul reading the one before it, 32 layers with their own weights) as queue
+launches, which is what a decode step pays at the boundaries between dependent matmuls; `byte_kernels`, the pack,
+unpack, relayout and tilize kernels on a 4096x14336 matrix against the same HBM peak; `prefill`, configs[2] on the
+tensor cores; `big`, one large matmul (Llama-3-70B gate shape) alone.
+
+--impl reference times the reference's CPU path on a bounded sample: NumPy block-float rounding + fp32 matmul. With
+--reference PATH (a checkout of the reference) the rounding is the reference's own gpt2.bfp (kind "reference"); without,
+its restatement in oracle/bfp_oracle.py (kind "port").
 """
-import argparse, ctypes, json, os, statistics, subprocess, sys, threading, time
+import argparse, ctypes, hashlib, json, os, statistics, subprocess, sys, threading, time
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -81,38 +89,72 @@ class Clocks:
     return {"sm_mhz": statistics.median(int(r[0]) for r in rows), "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
 
 
-def cpu_sample(seconds_hint=15):
-  """The reference's CPU path (NumPy block-float rounding + fp32 matmul, baretile/models/gpt2.py:19-30 and
-  baretile/models/llama.py:19-33,500-510) on a bounded sample of the sweep: 4096 x 14336, both formats, M = 1 and 8."""
+def reference_bfp(path):
+  """The block-float rounding the CPU leg uses: the reference's own gpt2.bfp when a checkout is given, else the oracle's
+  restatement of it. Returns (function(values, dtype) -> values, kind)."""
   from oracle import bfp_oracle as o
+  if path:
+    sys.path.insert(0, path)
+    from baretile.models import gpt2
+    return (lambda a, dtype: np.asarray(gpt2.bfp(a, dtype), np.float32)), "reference"
+  return (lambda a, dtype: o.bfp_values(a, dtype).astype(np.float32)), "port"
+
+
+def cpu_sample(path=None):
+  """The reference's CPU path (NumPy block-float rounding + fp32 matmul, baretile/models/gpt2.py:19-30 and
+  baretile/models/llama.py:19-33,500-510) on a bounded sample of the sweep: 4096 x 14336, both formats, M = 1 and 8.
+  Timed three ways: the rounding alone (the packer's CPU counterpart), the matmul on already dequantised weights, and
+  both together, which is what the GB/s figure is quoted on; and configs[0] (SmolLM MLP shape) as a time."""
+  from oracle import bfp_oracle as o
+  bfp, kind = reference_bfp(path)
   rng = np.random.default_rng(0)
   k, n = 4096, 14336
   w = o.bf16_floats(rounded(rng, (k, n), 0.02, True))
-  t0, total = time.perf_counter(), 0
+  total, t_pack, t_mm = 0, 0.0, 0.0
   for m in (1, 8):
     x = o.bf16_floats(rounded(rng, (m, k), 1.0))
     for fmt in FORMATS:
-      wd = o.dequant(w, fmt)                  # unpack: the weights as the values the format holds
+      t0 = time.perf_counter()
+      wd = np.concatenate([bfp(w[i:i + 1024], fmt) for i in range(0, k, 1024)])   # unpack: the weights as the values the format holds
+      t1 = time.perf_counter()
       o.matmul(x, wd, "none")
+      t2 = time.perf_counter()
+      t_pack, t_mm = t_pack + t1 - t0, t_mm + t2 - t1
       total += algorithmic_bytes(k, n, fmt, m, False)
-  dt = time.perf_counter() - t0
-  return total / dt / 1e9, dt, f"4096x14336 bfp8+bfp4, M=1 and 8: NumPy block-float dequantisation + fp32 matmul, {dt:.1f} s"
+  x0, w0 = o.bf16_floats(rounded(rng, (32, 576), 1.0)), o.bf16_floats(rounded(rng, (576, 1536), 0.02))
+  t0 = time.perf_counter()
+  for _ in range(20): o.matmul(x0, bfp(w0, "bfp8"), "relu")
+  cfg0_ms = (time.perf_counter() - t0) / 20 * 1e3
+  dt = t_pack + t_mm
+  detail = {"kind": kind, "pack_Mvalues_per_s": round(4 * k * n / t_pack / 1e6, 1), "matmul_on_dequantised_GBps": round(total / t_mm / 1e9, 3),
+            "dequant_plus_matmul_GBps": round(total / dt / 1e9, 3), "config0_relu_32x576x1536_bfp8_ms": round(cfg0_ms, 3)}
+  return total / dt / 1e9, dt, f"4096x14336 bfp8+bfp4, M=1 and 8: NumPy block-float rounding + fp32 matmul, {dt:.1f} s", detail
 
 
 def run_reference(args, rank):
   if rank != 0: return
   values, seconds = [], []
-  for _ in range(max(1, min(args.warmup, 1))): cpu_sample()
+  for _ in range(max(1, min(args.warmup, 1))): cpu_sample(args.reference)
   for _ in range(args.steps):
-    v, dt, sample = cpu_sample()
+    v, dt, sample, detail = cpu_sample(args.reference)
     values.append(v); seconds.append(dt)
   v = statistics.mean(values)
   print(json.dumps({"impl": "reference", "metric": "decode GEMV achieved HBM GB/s (bfp8/bfp4, Llama-3-8B shapes)", "value": v, "unit": "GB/s",
                     "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(seconds),
                     "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x bfp8/bfp4, fp32 accumulate", "data": "synthetic",
-                    "config": {"workload": "decode-gemv-sweep (configs[1]), bounded sample", "sample": sample},
-                    "cpu_baseline": {"value": v, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+                    "config": {"workload": "decode-gemv-sweep (configs[1]), bounded sample", "sample": sample, "cpu_detail": detail},
+                    "cpu_baseline": {"value": v, "unit": "GB/s", "cores": os.cpu_count(), "kind": detail["kind"], "sample": sample},
                     "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def recorded_traffic():
+  """DRAM read + write bytes of one 24-matmul launch, from the ncu capture summarised in profiles/: valid only for the
+  kernel source it was taken from, so the file names that source's hash; None when the source has changed since."""
+  try:
+    with open(os.path.join(ROOT, "profiles", "gemv_queue_kernel_sweep_traffic.json")) as f: rec = json.load(f)
+    with open(os.path.join(ROOT, "baretile_b200", "csrc", "gemv.cu"), "rb") as f: sha = hashlib.sha256(f.read()).hexdigest()
+    return rec["dram_bytes_per_launch"] if rec["gemv_cu_sha256"] == sha else None
+  except Exception: return None
 
 
 def main():
@@ -122,6 +164,8 @@ def main():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
   ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+  ap.add_argument("--reference", default="", help="a checkout of the reference: the CPU leg then uses its own gpt2.bfp")
+  ap.add_argument("--no-extras", action="store_true", help="headline and end-to-end only (profiling captures)")
   ap.add_argument("--quick", action="store_true", help="4096x4096 only (profiling captures)")
   ap.add_argument("--only", default="", help="run one case of the sweep, as KxN:fmt:M:pair, e.g. 4096x14336:bfp8:8:0 (profiling captures)")
   ap.add_argument("--prefill-rows", type=int, default=2048, help="rows of the prefill leg; 0 skips it")
@@ -150,16 +194,20 @@ def main():
     k, n = map(int, shape.split("x"))
     todo = [(k, n, fmt, int(m), bool(int(pair)))]
   weights, work = {}, []
+  sources = {}
   def weight(k, n, fmt, role):
     if (k, n, fmt, role) not in weights:
-      weights[k, n, fmt, role] = Tensor.frombytes(rt, k, n, rounded(rng, (k, n), 0.02, True).tobytes()).cast(fmt).columns()
+      bits = rounded(rng, (k, n), 0.02, True).tobytes()
+      if (k, n) == (4096, 4096): sources[k, n, fmt, role] = bits          # kept for the check against the oracle below
+      weights[k, n, fmt, role] = Tensor.frombytes(rt, k, n, bits).cast(fmt).columns()
     return weights[k, n, fmt, role]
   for k, n, fmt, m, pair in todo:
     xh = rounded(rng, (m, k), 1.0)
     x = Tensor.frombytes(rt, m, k, xh.tobytes())
     w = weight(k, n, fmt, "gate" if pair else "w")
     w2 = weight(k, n, fmt, "up") if pair else None
-    work.append(dict(k=k, n=n, fmt=fmt, m=m, pair=pair, x=x, xh=xh, w=w, w2=w2, bytes=algorithmic_bytes(k, n, fmt, m, pair)))
+    work.append(dict(k=k, n=n, fmt=fmt, m=m, pair=pair, x=x, xh=xh, w=w, w2=w2, bytes=algorithmic_bytes(k, n, fmt, m, pair),
+                     w_source=sources.get((k, n, fmt, "w"))))
   rt.wait()
   step_bytes = sum(c["bytes"] for c in work)
 
@@ -203,15 +251,27 @@ def main():
   ms_per_step = ms / args.steps
   value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
+  # ---- what the replays computed is what the oracle computes: one replayed result per format ----
+  from oracle import bfp_oracle as o
+  checked = {}
+  for c, y in zip(work, outs):
+    if c["fmt"] in checked or c["pair"] or c["k"] != 4096 or c["n"] != 4096: continue
+    wd = o.bf16_floats(np.frombuffer(c["w_source"], np.uint16).reshape(c["k"], c["n"]))
+    ref = o.bf16_floats(c["xh"]).astype(np.float32) @ o.dequant(wd, c["fmt"])
+    checked[c["fmt"]] = round(o.rel_err(y.numpy(), ref), 5)
+    assert checked[c["fmt"]] <= 1e-2, ("replayed result differs from the oracle", c, checked)
+
   # ---- per-launch durations, for the roofline: events around every launch of a plain (not replayed) step ----
   pairs = [(ctypes.c_uint64(), ctypes.c_uint64()) for _ in work]
   for a, b in pairs:
     _lib.call("bt_event_create", dev, ctypes.byref(a)); _lib.call("bt_event_create", dev, ctypes.byref(b))
   per = [[] for _ in work]
-  blocker_bytes = 4 << 30                    # a memset long enough that the launches below queue up behind it
-  blocker = rt.dram_alloc(blocker_bytes)
+  # a copy to host memory long enough that the launches below queue up behind it (a read: a memset would leave the L2
+  # full of dirty lines, and their write-back would slow the launches that follow it)
+  blocker_bytes = 64 << 20
+  blocker, blocker_host = rt.dram_alloc(blocker_bytes), rt.host_alloc(blocker_bytes)
   for rep in range(args.warmup + max(5, min(args.steps, 20))):
-    _lib.call("bt_memset", dev, blocker, 0, blocker_bytes, rt.stream)
+    rt.download_async(blocker_host, blocker)
     for (a, b), (kernel, kargs, _, _) in zip(pairs, recorded):
       _lib.call("bt_event_record", dev, a, rt.stream)
       _lib.call(kernel, dev, *kargs, rt.stream)
@@ -223,9 +283,8 @@ def main():
       _lib.call("bt_event_elapsed_ms", dev, a, b, ctypes.byref(t))
       per[i].append(t.value)
   peak, peak_kind = peaks()
-  # DRAM read + write bytes of one 24-matmul launch, from an ncu capture of this command (its launch list is summarised under profiles/);
-  # it belongs to the full sweep only
-  traffic = 1_315_175_744 if len(work) == 24 and world == 1 else None
+  # DRAM read + write bytes of one 24-matmul launch, from an ncu capture of this command; it belongs to the full sweep only
+  traffic = recorded_traffic() if len(work) == 24 and world == 1 else None
   table, total_t = [], 0.0
   for c, ts in zip(work, per):
     t = statistics.median(ts)
@@ -273,9 +332,102 @@ def main():
   e2e = world * step_bytes / e2e_s / 1e9
   clock = clocks.stop() if clocks else None
 
+  extras = world == 1 and not args.quick and not args.only and not args.no_extras
+
+  # ---- a decode layer chain: every matmul reads the one before it (what a decode step pays at the boundaries) ----
+  chain = None
+  if extras:
+    chain = []
+    layers = 32
+    for fmt in FORMATS:
+      base = [weight(4096, 4096, fmt, "w"), weight(4096, 14336, fmt, "gate"), weight(4096, 14336, fmt, "up"), weight(14336, 4096, fmt, "w")]
+      stack = []
+      for _ in range(layers):                       # every layer streams its own copy: 32 layers are 3.5 to 6.6 GB of weights
+        copies = []
+        for b in base:
+          t = Tensor(rt, b.rows, b.cols, dtype=fmt)
+          t.runs = b.runs
+          rt.launch("bt_d2d", (t.addr, b.addr, b.tiles * TILE[fmt]), name="copy")
+          copies.append(t)
+        stack.append(copies)
+      chain_bytes = layers * sum(b.tiles * TILE[fmt] for b in base)
+      for m in (1, 8):
+        h0 = Tensor.frombytes(rt, m, 4096, rounded(rng, (m, 4096), 1.0).tobytes())
+        with rt.record() as chain_step:
+          h = h0
+          with rt.queue():
+            for wo, wg, wu, wd in stack:
+              a = (h @ wo).realize()
+              g = ((a @ wg).silu() * (a @ wu)).realize()
+              h = (g @ wd).realize()
+        for _ in range(2): chain_step.replay()
+        reps = 3
+        cms = timed(chain_step.replay, reps) / reps
+        chain.append({"fmt": fmt, "M": m, "matmuls": 3 * layers, "us_per_matmul": round(cms * 1e3 / (3 * layers), 2), "GBps": round(chain_bytes / (cms * 1e-3) / 1e9, 1),
+                      "frac": round(chain_bytes / (cms * 1e-3) / 1e9 / peak, 3)})
+        chain_step.close()
+        del h, a, g, h0
+      del stack
+
+  # ---- one large matmul alone (Llama-3-70B gate shape, 8192 x 28672): the kernel without the boundaries ----
+  big = None
+  if extras:
+    big = []
+    for fmt in FORMATS:
+      src = weight(4096, 14336, fmt, "gate")
+      ws = []
+      for _ in range(3):                              # three copies taken in turn: none finds its bytes in L2
+        t = Tensor(rt, 8192, 28672, dtype=fmt)
+        t.runs = (-(-t.tc // 4), t.tr, 0)
+        for part in range(4): rt.launch("bt_d2d", (t.addr + part * src.tiles * TILE[fmt], src.addr, src.tiles * TILE[fmt]), name="copy")
+        ws.append(t)
+      for m in (1, 8):
+        xb = Tensor.frombytes(rt, m, 8192, rounded(rng, (m, 8192), 1.0).tobytes())
+        with rt.record() as big_step:
+          ys = [(xb @ w).realize() for w in ws]
+        for _ in range(2): big_step.replay()
+        reps = 5
+        bms = timed(big_step.replay, reps) / (reps * len(ws))
+        nbytes = algorithmic_bytes(8192, 28672, fmt, m, False)
+        big.append({"K": 8192, "N": 28672, "fmt": fmt, "M": m, "us": round(bms * 1e3, 2), "GBps": round(nbytes / (bms * 1e-3) / 1e9, 1), "frac": round(nbytes / (bms * 1e-3) / 1e9 / peak, 3)})
+        big_step.close()
+        del ys, xb
+      del ws
+
+  # ---- the byte kernels either side of the matmul, on a 4096 x 14336 matrix, against the same HBM peak ----
+  byte_kernels = None
+  if extras:
+    byte_kernels = []
+    k, n = 4096, 14336
+    values = k * n
+    flats = [rt.dram_alloc(2 * values) for _ in range(3)]
+    tiles = [Tensor(rt, k, n) for _ in range(3)]
+    for f in flats: rt.launch("bt_d2d", (f, weights[k, n, "bfp8", "w"].addr, values), name="copy")    # any bytes will do for a layout kernel
+    def time_kernel(name, bytes_per_value, launches):
+      for fn in launches: fn()
+      reps = 4
+      kms = timed(lambda: [fn() for fn in launches], reps) / (reps * len(launches))
+      gbps = bytes_per_value * values / (kms * 1e-3) / 1e9
+      byte_kernels.append({"kernel": name, "bytes_per_value": bytes_per_value, "us": round(kms * 1e3, 1), "GBps": round(gbps, 1), "frac": round(gbps / peak, 3)})
+    time_kernel("tilize_kernel<bf16>", 4.0, [lambda f=f, t=t: rt.launch("bt_tilize", (2, f, t.addr, 1, k, n), name="upload") for f, t in zip(flats, tiles)])
+    for t, bits in zip(tiles, range(3)): rt.launch("bt_tilize", (2, flats[0], t.addr, 1, k, n), name="upload")
+    real = Tensor.frombytes(rt, k, n, rounded(rng, (k, n), 0.02, True).tobytes())
+    for t in tiles: rt.launch("bt_d2d", (t.addr, real.addr, 2 * values), name="copy")
+    for fmt in FORMATS:
+      tb = TILE[fmt] / 1024
+      packed = [Tensor(rt, k, n, dtype=fmt) for _ in range(3)]
+      streamed = [Tensor(rt, k, n, dtype=fmt) for _ in range(3)]
+      code = int(fmt[3])
+      time_kernel(f"pack_kernel<{fmt}>", 2 + tb, [lambda t=t, q=q: rt.launch("bt_pack_bfp", (code, t.addr, q.addr, t.tiles), name=fmt) for t, q in zip(tiles, packed)])
+      time_kernel(f"relayout_kernel<{fmt}>", 2 * tb, [lambda q=q, z=z: rt.launch("bt_relayout", (code, 1, q.tr, q.tc, q.addr, z.addr), name="columns") for q, z in zip(packed, streamed)])
+      time_kernel(f"unpack_kernel<{fmt}>", 2 + tb, [lambda t=t, q=q: rt.launch("bt_unpack_bfp", (code, q.addr, t.addr, t.tiles), name="storage") for t, q in zip(tiles, packed)])
+      del packed, streamed
+    for f in flats: rt.dram_free(f)
+    del tiles, real
+
   # ---- the prefill configuration (configs[2]) on the tensor cores: reported beside the headline, 1 GPU ----
   prefill = None
-  if world == 1 and not args.quick and args.prefill_rows > 0:
+  if extras and args.prefill_rows > 0:
     M = args.prefill_rows
     xp = Tensor.frombytes(rt, M, 4096, rounded(rng, (M, 4096), 1.0).tobytes())
     wg, wu, wd = weight(4096, 14336, "bfp8", "gate"), weight(4096, 14336, "bfp8", "up"), weight(14336, 4096, "bfp4", "w")
@@ -335,7 +487,10 @@ def main():
             "vs_baseline": None, "dtype": "bf16 x bfp8/bfp4, fp32 accumulate", "data": "synthetic",
             "config": {"workload": "decode-gemv-sweep (configs[1]): K x N in {4096x4096, 4096x14336, 14336x4096} x {bfp8, bfp4} x M in {1, 8, 32} + fused gate/up pair",
                        "matmuls_per_step": len(work), "launches_per_step": kernels_per_step, "bytes_per_step": step_bytes, "l2": "a step reads 410 MB of distinct weights (> 3x L2); no buffer is reused within 2x L2 of traffic",
-                       "timing": "CUDA events on the launching stream around K replays of the recorded step; max over ranks"},
+                       "timing": "CUDA events on the launching stream around K replays of the recorded step; max over ranks",
+                       "replay_vs_oracle_rel_err": checked,
+                       "chain": chain, "chain_note": "Llama-3-8B decode layers, o-proj -> fused gate/up -> down, each reading the one before it, 32 layers of distinct weights, as bt_gemv_queue launches of 32; frac is of the same HBM peak",
+                       "big": big, "byte_kernels": byte_kernels, "prefill": prefill, "sharded": sharded},
             "clocks": clock,
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                     "ms_per_step": round(e2e_s * 1e3, 3)},
@@ -344,10 +499,10 @@ def main():
                          "of": peak_kind, "kernel": "gemv_queue_kernel: a step is one launch that runs the 24 matmuls in order; bytes per launch / launch duration averaged over the event-timed region",
                          "per_launch_events_GBps": round(per_launch_sum, 1),
                          "frac_of_spec_8TBps": round(achieved / 8000, 3)},
-            "prefill": prefill, "sharded": sharded, "cases": table}
+            "cases": table}
     if not args.no_cpu:
-      v, dt, sample = cpu_sample()
-      line["cpu_baseline"] = {"value": round(v, 3), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample}
+      v, dt, sample, detail = cpu_sample(args.reference)
+      line["cpu_baseline"] = {"value": round(v, 3), "unit": "GB/s", "cores": os.cpu_count(), "kind": detail["kind"], "sample": sample, "detail": detail}
     print(json.dumps(line))
   rt.close()
   if dist is not None: dist.destroy_process_group()
