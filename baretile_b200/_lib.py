@@ -57,6 +57,13 @@ SIGNATURES = {
   "bt_gemv_check": [i32, u64, u64, ctypes.POINTER(i32)],
   "bt_gemv_queue": [i32, i32, ctypes.POINTER(GemvOp), u64, size_t, u64],
   "bt_gemv_queue_plan": [i32, ctypes.POINTER(GemvOp), ctypes.POINTER(i32)],
+  "bt_comm_unique_id": [vp, size_t],
+  "bt_comm_init": [i32, i32, i32, vp, ctypes.POINTER(u64)],
+  "bt_comm_destroy": [u64],
+  "bt_allgather": [i32, u64, u64, u64, size_t, u64],
+  "bt_allreduce_sum": [i32, u64, u64, size_t, u64],
+  "bt_round_tilize": [i32, u64, u64, i32, i32, u64],
+  "bt_argmax_combine": [i32, u64, i32, i32, u64, u64, u64],
   "bt_launch_count": [ctypes.POINTER(u64)],
 }
 

@@ -70,10 +70,9 @@ constexpr size_t kWsError = 0;                                   // int: set to 
 constexpr size_t kWsOpsDone = 8;                                 // int[kQueueMax]: CTAs that finished each matmul of the launch
 constexpr size_t kWsSets = 256;                                  // the sets start here
 constexpr size_t kSetPanelsDone = 0;                             // int: sub-panels finished (argmax epilogue)
-constexpr size_t kSetCounters = 256;                             // int[kMaxSubPanels]: CTAs arrived at a sub-panel
-constexpr size_t kSetArgVal = kSetCounters + 4 * kMaxSubPanels;  // float[kMaxSubPanels][32]
-constexpr size_t kSetArgIdx = kSetArgVal + 4 * 32 * kMaxSubPanels;   // int[kMaxSubPanels][32]
-constexpr size_t kSetPartials = kSetArgIdx + 4 * 32 * kMaxSubPanels;
+constexpr size_t kSetKeys = 256;                                 // u64[32]: per token the best (value, column) so far (argmax epilogue)
+constexpr size_t kSetCounters = 512;                             // int[kMaxSubPanels]: CTAs arrived at a sub-panel
+constexpr size_t kSetPartials = kSetCounters + 4 * kMaxSubPanels;
 constexpr size_t kSlotFloatsMax = 8 * 32 * 32;                   // 8 warps x up to 32 accumulators x 32 lanes
 constexpr size_t kSetBytes = kSetPartials + (size_t)kMaxCtas * kSlotFloatsMax * 4;
 constexpr int kSets = 2;                                         // matmuls of a queue in flight at most
@@ -119,12 +118,12 @@ struct GemvParams {
   int per;                    // units per range when ranges are cut to fit the sub-panels; 0: equal shares of all CTAs
 };
 
-// What a matmul uses while it runs: the count of finished sub-panels (argmax), the arrivals per sub-panel (both
-// zero before first use; the kernel leaves them zero), per-sub-panel argmax candidates and one slot of partial sums
-// per CTA.
+// What a matmul uses while it runs: the count of finished sub-panels and the per-token best keys (argmax), the
+// arrivals per sub-panel (all zero before first use; the kernel leaves them zero) and one slot of partial sums per CTA.
 struct Scratch {
-  int *panels_done, *counters, *part_idx;
-  float *part_val, *partials;
+  int *panels_done, *counters;
+  unsigned long long *keys;   // per token the best (value, column) so far, as an ordered key; zero: nothing yet
+  float *partials;
 };
 
 // What one launch gets: the matmuls and the scratch they share: a wait-gave-up flag, the counts of CTAs that
@@ -245,6 +244,13 @@ __device__ __forceinline__ uint32_t bf16_half_up(float v) { return (__float_as_u
 __device__ __forceinline__ float bf16_value(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
 // a beats b: larger value, or the same value at a lower column; -0 equals 0; a NaN never wins
 __device__ __forceinline__ bool beats(float av, int ai, float bv, int bi) { return av > bv || (av == bv && ai < bi); }
+// (value, column) as one number whose order is `beats`: larger value first, then the lower column. Zero is reserved
+// for "nothing yet"; no value maps to it, since a NaN is never offered and -inf maps to 0x007FFFFF in the upper half.
+__device__ __forceinline__ unsigned long long pick_key(float v, int column) {
+  uint32_t b = __float_as_uint(v == 0.f ? 0.f : v);
+  b ^= b >> 31 ? 0xFFFFFFFFu : 0x80000000u;
+  return (unsigned long long)b << 32 | (0xFFFFFFFFu - (uint32_t)column);
+}
 
 
 // The epilogue of one finished tile column. Lane (g, t) holds, for each channel group ng and token group tg,
@@ -283,6 +289,11 @@ __device__ __forceinline__ void finish_column(const GemvParams &p, const float (
             if (beats(v0, n0, best_v[tgs][j], best_i[tgs][j])) best_v[tgs][j] = v0, best_i[tgs][j] = n0;
             if (beats(v1, n0 + 1, best_v[tgs][j], best_i[tgs][j])) best_v[tgs][j] = v1, best_i[tgs][j] = n0 + 1;
           }
+          continue;
+        }
+        if (p.out_fp32 == 2) {
+          // row-major fp32, only the rows there are: partial sums on their way to an all-reduce
+          if (tg <= kLast && m < p.M) *reinterpret_cast<float2 *>(static_cast<float *>(p.out) + (size_t)m * (p.TC * 32) + col * 32 + 16 * ng + 2 * g) = make_float2(v0, v1);
           continue;
         }
         if (!valid) v0 = v1 = 0.f;
@@ -650,22 +661,25 @@ __device__ __forceinline__ void consume(const Queue &q, const GemvParams &p, con
             int i = arg_i[lane];
             for (int c = 1; c < wcols; c++)
               if (beats(arg_v[c * 32 + lane], arg_i[c * 32 + lane], v, i)) v = arg_v[c * 32 + lane], i = arg_i[c * 32 + lane];
-            sc.part_val[done_sp * 32 + lane] = v, sc.part_idx[done_sp * 32 + lane] = i;
-            fence_gpu();
+            // offer it to the token's key: a maximum over all sub-panels whatever the order they finish in, so the last
+            // one to finish has the answer at hand instead of a pass over every sub-panel's candidates
+            if (lane < p.M && i != 0x7FFFFFFF) atomicMax(sc.keys + lane, pick_key(v, i));
+            __syncwarp();
             int is_last = 0;
-            if (lane == 0) is_last = atomicAdd(sc.panels_done, 1) == subpanels - 1;
+            if (lane == 0) {
+              fence_gpu();
+              is_last = atomicAdd(sc.panels_done, 1) == subpanels - 1;
+            }
             is_last = __shfl_sync(0xFFFFFFFFu, is_last, 0);
             if (is_last) {
+              // turns the keys into the answer and leaves the scratch as it found it
               fence_gpu();
               if (lane < p.M) {
-                float bv = -INFINITY;
-                int bi = 0x7FFFFFFF;
-                for (int s2 = 0; s2 < subpanels; s2++) {
-                  const float ov = __ldcg(sc.part_val + s2 * 32 + lane);
-                  const int oi = __ldcg(sc.part_idx + s2 * 32 + lane);
-                  if (beats(ov, oi, bv, bi)) bv = ov, bi = oi;
-                }
-                p.arg_val[lane] = bv, p.arg_idx[lane] = bi + p.arg_base;
+                const unsigned long long key = atomicExch(sc.keys + lane, 0ull);
+                uint32_t b = (uint32_t)(key >> 32);
+                b ^= b >> 31 ? 0x80000000u : 0xFFFFFFFFu;
+                p.arg_val[lane] = key ? __uint_as_float(b) : -INFINITY;
+                p.arg_idx[lane] = (key ? (int)(0xFFFFFFFFu - (uint32_t)key) : 0x7FFFFFFF) + p.arg_base;
               }
               if (lane == 0) *sc.panels_done = 0;
             }
@@ -749,7 +763,7 @@ int check_op(const char *who, int index, const bt_gemv_op &o) {
   BT_REQUIRE((o.epilogue == BT_EPI_GLU) == (o.w2 != 0) && o.w2 % 16 == 0, "%s: matmul %d: w2 goes with the GLU epilogue, and only with it", who, index);
   BT_REQUIRE(o.add % 4 == 0, "%s: matmul %d: the addend must be 4-byte aligned", who, index);
   if (o.epilogue == BT_EPI_ARGMAX) BT_REQUIRE(o.arg_val && o.arg_idx, "%s: matmul %d: the argmax epilogue needs arg_val and arg_idx", who, index);
-  else BT_REQUIRE(o.out && o.out % 8 == 0 && (o.out_dtype == BT_BF16 || o.out_dtype == BT_FP32), "%s: matmul %d: needs an 8-byte aligned bf16 or fp32 result", who, index);
+  else BT_REQUIRE(o.out && o.out % 8 == 0 && (o.out_dtype == BT_BF16 || o.out_dtype == BT_FP32 || o.out_dtype == BT_FP32_ROWS), "%s: matmul %d: needs an 8-byte aligned bf16 or fp32 result", who, index);
   return BT_OK;
 }
 
@@ -767,6 +781,7 @@ int ranges_read(const bt_gemv_op &o, Range *r) {
 int ranges_written(const bt_gemv_op &o, Range *r) {
   int n = 0;
   if (o.epilogue == BT_EPI_ARGMAX) r[n++] = {o.arg_val, o.arg_val + 4ull * o.M}, r[n++] = {o.arg_idx, o.arg_idx + 4ull * o.M};
+  else if (o.out_dtype == BT_FP32_ROWS) r[n++] = {o.out, o.out + 4ull * o.M * o.N};
   else r[n++] = {o.out, o.out + (uint64_t)(o.N / 32) * (o.out_dtype == BT_FP32 ? 4096 : 2048)};
   return n;
 }
@@ -857,7 +872,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
       GemvParams &p = q.op[i];
       p.x = as_ptr<uint8_t>(o.x), p.w[0] = as_ptr<uint8_t>(o.w), p.w[1] = as_ptr<uint8_t>(o.w2), p.add = as_ptr<uint16_t>(o.add);
       p.out = as_ptr<void>(o.out), p.arg_val = as_ptr<float>(o.arg_val), p.arg_idx = as_ptr<int>(o.arg_idx);
-      p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32;
+      p.alpha = o.alpha, p.arg_base = o.arg_base, p.M = o.M, p.KT = o.K / 32, p.TC = o.N / 32, p.epi = o.epilogue, p.out_fp32 = o.out_dtype == BT_FP32 ? 1 : o.out_dtype == BT_FP32_ROWS ? 2 : 0;
       p.fmt = o.fmt, p.pair = o.epilogue == BT_EPI_GLU, p.tg = o.M <= 8 ? 1 : o.M <= 16 ? 2 : 4;
       p.wait_for = wait_for(ops + base, i, scratch.sets);
       p.turn = (int)(((long long)(base + i) * 101) % ctas);
@@ -883,7 +898,7 @@ int enqueue(const char *who, int device, int n, const bt_gemv_op *ops, const Que
 Scratch scratch_at(unsigned char *set) {
   Scratch s;
   s.panels_done = reinterpret_cast<int *>(set + kSetPanelsDone), s.counters = reinterpret_cast<int *>(set + kSetCounters);
-  s.part_val = reinterpret_cast<float *>(set + kSetArgVal), s.part_idx = reinterpret_cast<int *>(set + kSetArgIdx);
+  s.keys = reinterpret_cast<unsigned long long *>(set + kSetKeys);
   s.partials = reinterpret_cast<float *>(set + kSetPartials);
   return s;
 }
@@ -908,12 +923,11 @@ Queue workspace_scratch(uint64_t work) {
 namespace {
 constexpr int kStaticSubPanels = 4096;                                  // N <= 4096 * 4 * 32 = 524288 columns
 constexpr size_t kStaticSlotFloats = 8 * 8 * 32;                        // 8 warps, 8 accumulators per lane
-constexpr size_t kStCounters = 256;
+constexpr size_t kStKeys = 256;
+constexpr size_t kStCounters = 512;
 constexpr size_t kStControlBytes = kStCounters + 4 * (size_t)kStaticSubPanels;   // what must be zero when a call starts
-constexpr size_t kStArgVal = kStControlBytes;
-constexpr size_t kStArgIdx = kStArgVal + 4 * 32 * (size_t)kStaticSubPanels;
-constexpr size_t kStPartials = kStArgIdx + 4 * 32 * (size_t)kStaticSubPanels;
-constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 3.7 MB
+constexpr size_t kStPartials = kStControlBytes;
+constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 0.7 MB
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
@@ -984,7 +998,7 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
   scratch.error = reinterpret_cast<int *>(base + kWsError), scratch.ops_done = reinterpret_cast<int *>(base + kWsOpsDone);
   scratch.sets = 1;
   scratch.set[0].panels_done = reinterpret_cast<int *>(base + 192), scratch.set[0].counters = reinterpret_cast<int *>(base + kStCounters);
-  scratch.set[0].part_val = reinterpret_cast<float *>(base + kStArgVal), scratch.set[0].part_idx = reinterpret_cast<int *>(base + kStArgIdx);
+  scratch.set[0].keys = reinterpret_cast<unsigned long long *>(base + kStKeys);
   scratch.set[0].partials = reinterpret_cast<float *>(base + kStPartials);
   scratch.slot_floats = (int)kStaticSlotFloats;
   return enqueue("bt_gemv_bfp_static", device, 1, &op, scratch, stream);

@@ -1,7 +1,8 @@
 """Layers too large for one GPU: the block-float matmul path sharded over the GPUs of one box.
 
-One process per GPU (torchrun); `torch.distributed` carries the exchanges, NCCL over NVLink on GPUs and gloo in the
-CPU tests. The reference has no collective backend -- its only inter-chip transport is a point-to-point tensor copy
+One process per GPU (torchrun). On GPUs the exchanges are NCCL collectives behind the library's C-ABI (bt_allgather,
+bt_allreduce_sum, bt_argmax_combine), queued on the runtime's stream between the matmul launches; the same rules as
+plain host functions over `torch.distributed` (gloo) are what the CPU tests run. The reference has no collective backend -- its only inter-chip transport is a point-to-point tensor copy
 over Ethernet (`Tensor.to`, baretile/tensor.py:708-726) -- so the partitioning here follows the shapes of the path:
 
   gate/up   W[K, N] split over N in whole tile columns; x is replicated; SiLU(x Wg) * (x Wu) is local to a rank;
@@ -14,7 +15,7 @@ over Ethernet (`Tensor.to`, baretile/tensor.py:708-726) -- so the partitioning h
             (larger value wins, of equal values the lower index; topk_kernel, baretile/kernels.py:1173-1231).
 
 The functions in the first half are pure host logic and work on any backend; the classes in the second half drive
-the CUDA kernels through the Tensor API and share the runtime's stream with the collectives.
+the CUDA kernels and the collectives through the C-ABI on the runtime's stream.
 """
 import torch
 import torch.distributed as dist
@@ -76,69 +77,87 @@ def gather_argmax(values, indices, group=None):
 
 
 # ---- the sharded layers on GPUs -----------------------------------------------------------------------------------
+# Everything below goes through the C-ABI on the runtime's stream: matmul launches, NCCL collectives (bt_allgather,
+# bt_allreduce_sum) and the small kernels either side of them, with no torch operation on the data path.
 
-def _stream(rt):
-  """The runtime's CUDA stream as a torch stream, so collectives queue in order with the kernels."""
-  return torch.cuda.ExternalStream(rt.stream, device=torch.device("cuda", rt.device))
+class Comm:
+  """The ranks' NCCL communicator behind the C-ABI (bt_comm_init). `exchange(bytes)` hands rank 0's bytes to every
+  rank: by default over torch.distributed (any backend), which is only used for this one hand-shake."""
+  def __init__(self, rt, rank, world, exchange=None):
+    import ctypes
+    from baretile_b200 import _lib
+    self.rt, self.rank, self.world = rt, rank, world
+    uid = ctypes.create_string_buffer(128)
+    if rank == 0: _lib.call("bt_comm_unique_id", uid, 128)
+    if exchange is None:
+      def exchange(data):
+        box = [data]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+    uid = ctypes.create_string_buffer(exchange(uid.raw), 128)
+    handle = ctypes.c_uint64()
+    _lib.call("bt_comm_init", rt.device, rank, world, uid, ctypes.byref(handle))
+    self.handle = handle.value
 
-
-def _rows(rt, t, dtype):
-  """A realized Tensor's values as a row-major torch tensor on the runtime's stream (fp32 or bf16)."""
-  out = torch.empty((t.rows, t.cols), dtype=dtype, device=torch.device("cuda", rt.device))
-  rt.launch("bt_untilize", (out.element_size(), t.addr, out.data_ptr(), 1, t.rows, t.cols), name="readback")
-  return out
-
-
-def _tensor(rt, rows, dtype="bf16"):
-  """A row-major torch tensor (bf16, or fp32 to be rounded to bf16) as a bf16 Tensor in tile layout."""
-  from baretile_b200.tensor import Tensor
-  t = Tensor(rt, rows.shape[0], rows.shape[1], dtype=dtype)
-  src = rows.contiguous()
-  if src.dtype == torch.float32:
-    half = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
-    rt.launch("bt_round_bf16", (src.data_ptr(), half.data_ptr(), src.numel()), name="round")
-    src = half
-  rt.launch("bt_tilize", (2, src.data_ptr(), t.addr, 1, t.rows, t.cols), name="upload")
-  t._keep = (rows, src)    # the launches above read these buffers
-  return t
+  def close(self):
+    from baretile_b200 import _lib
+    if self.handle: _lib.lib().bt_comm_destroy(self.handle)
+    self.handle = 0
 
 
 class ShardedMLP:
-  """SwiGLU MLP over the ranks of a process group: gate/up split over N, down split over K.
+  """SwiGLU MLP over the ranks: gate/up split over N, down split over K.
 
   `wg`, `wu` are this rank's [K, N/world] column slices and `wd` its [N/world, K_out] row slice, as block-float
   Tensors by columns. forward(x) takes the replicated bf16 activations [M, K] (M <= 32) and returns the [M, K_out]
-  result as a bf16 Tensor on every rank. With gather=True the gate/up result is all-gathered to [M, N] first, as a
-  stand-alone column-parallel layer would do, and the rank then multiplies its own slice of it; with gather=False
-  the local slice feeds the down projection directly (column-parallel into row-parallel needs no exchange)."""
-  def __init__(self, rt, wg, wu, wd, group=None):
-    self.rt, self.wg, self.wu, self.wd, self.group = rt, wg, wu, wd, group
-    self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+  result as a bf16 Tensor on every rank: the gate/up pair and the down projection leave as one queue launch, the down
+  projection writes fp32 partial sums row-major, one all-reduce adds them over the ranks and one small kernel rounds
+  them to bf16 tiles. With gather=True the gate/up result is also all-gathered to [M, N], as a stand-alone
+  column-parallel layer would do (the tile buffers of the ranks, one after another, are the full tensor's tile row);
+  the down projection needs only the rank's own slice either way."""
+  def __init__(self, rt, wg, wu, wd, comm):
+    self.rt, self.wg, self.wu, self.wd, self.comm = rt, wg, wu, wd, comm
+    self.partial = rt.dram_alloc(4 * 32 * wd.cols)
+    self.gathered = None
 
-  def forward(self, x, gather=True):
-    rt = self.rt
-    with torch.cuda.stream(_stream(rt)):
-      h = ((x @ self.wg).silu() * (x @ self.wu)).realize()              # [M, N/world] bf16, one launch
-      if gather:
-        full = all_gather_columns(_rows(rt, h, torch.bfloat16), group=self.group)
-        n = h.cols
-        h = _tensor(rt, full[:, self.rank * n:(self.rank + 1) * n])
-      partial = _rows(rt, h.matmul(self.wd, dtype="fp32").realize(), torch.float32)
-      return _tensor(rt, all_reduce_sum(partial, self.group))
+  def forward(self, x, gather=False):
+    import ctypes
+    from baretile_b200.tensor import Tensor, FMT_CODE
+    rt, m = self.rt, x.rows
+    out = Tensor(rt, m, self.wd.cols)
+    with rt.queue():
+      h = ((x @ self.wg).silu() * (x @ self.wu)).realize()              # [M, N/world] bf16 tiles
+      rt.launch("bt_gemv_bfp", (FMT_CODE[self.wd.dtype], 0, m, h.cols, self.wd.cols, h.addr, self.wd.addr, 0, 0, ctypes.c_float(1.0),
+                                self.partial, 16, 0, 0, 0, rt.work, rt.work_bytes), name="matmul down partial")
+    if gather:
+      if self.gathered is None or self.gathered.cols != h.cols * self.comm.world: self.gathered = Tensor(rt, 32, h.cols * self.comm.world)
+      rt.launch("bt_allgather", (self.comm.handle, h.addr, self.gathered.addr, h.tiles * 2048), name="all-gather")
+    rt.launch("bt_allreduce_sum", (self.comm.handle, self.partial, m * self.wd.cols), name="all-reduce")
+    rt.launch("bt_round_tilize", (self.partial, out.addr, m, self.wd.cols), name="round")
+    self.h = h                                                         # its memory is read by the launches above
+    return out
 
 
 class ShardedHead:
   """Greedy pick over a vocabulary split across the ranks: `w` is this rank's [K, V/world] slice by columns and
-  `base` the global index of its first column. pick(x) returns (values[M] fp32, indices[M] int32) torch tensors,
-  identical on every rank."""
-  def __init__(self, rt, w, base, group=None):
-    self.rt, self.w, self.base, self.group = rt, w, base, group
+  `base` the global index of its first column. pick(x) queues the matmul with its fused pick, the all-gather of the
+  ranks' 256-byte candidate blocks and the combining kernel, and returns the device address of the result: M fp32
+  values followed, 128 bytes in, by M int32 indices, identical on every rank. read() brings them to the host."""
+  def __init__(self, rt, w, base, comm):
+    self.rt, self.w, self.base, self.comm = rt, w, base, comm
+    self.mine, self.all, self.out = rt.dram_alloc(256), rt.dram_alloc(256 * comm.world), rt.dram_alloc(256)
 
   def pick(self, x):
-    from baretile_b200.tensor import _launch_matmul, _linear
+    import ctypes
+    from baretile_b200.tensor import FMT_CODE
     rt, m = self.rt, x.rows
-    dev = torch.device("cuda", rt.device)
-    vals, ids = torch.empty(32, dtype=torch.float32, device=dev), torch.empty(32, dtype=torch.int32, device=dev)
-    with torch.cuda.stream(_stream(rt)):
-      _launch_matmul(rt, _linear(x @ self.w), "argmax", None, m, arg=(vals.data_ptr(), ids.data_ptr()), arg_base=self.base)
-      return gather_argmax(vals[:m], ids[:m], self.group)
+    rt.launch("bt_gemv_bfp", (FMT_CODE[self.w.dtype], 4, m, x.cols, self.w.cols, x.addr, self.w.addr, 0, 0, ctypes.c_float(1.0), 0, 0,
+                              self.mine, self.mine + 128, self.base, rt.work, rt.work_bytes), name="matmul pick")
+    rt.launch("bt_allgather", (self.comm.handle, self.mine, self.all, 256), name="all-gather")
+    rt.launch("bt_argmax_combine", (self.all, self.comm.world, m, self.out, self.out + 128), name="combine")
+    return self.out
+
+  def read(self, m):
+    import numpy as np
+    raw = self.rt.download(self.out, 256)
+    return np.frombuffer(raw[:4 * m], np.float32).copy(), np.frombuffer(raw[128:128 + 4 * m], np.int32).copy()

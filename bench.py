@@ -448,37 +448,48 @@ def main():
                "includes": "the row-major copy of x and of h that feeds the TMA loads (2 small launches per step)"}
 
   # ---- the sharded configurations (configs[3], configs[4]): layers split over the ranks, with their exchanges ----
+  # Every rank holds its slice of the weights; the matmul launches, the NCCL collectives and the combining kernels
+  # are queued through the C-ABI on the runtime's stream. Times are CUDA events, the maximum over ranks; `ideal_us`
+  # is the rank's packed weight bytes at the measured HBM peak (the exchanges are latency, not bandwidth).
   sharded = None
   if dist is not None:
     from baretile_b200 import dist as bd
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)                     # NCCL may announce its version on stdout, which carries the one JSON line
+    try: comm = bd.Comm(rt, rank, world)
+    finally:
+      os.dup2(keep, 1)
+      os.close(keep)
     def tiled(rows, cols, seed):      # bf16 bits of a rows x cols matrix, a 1024 x 1024 N(0, 0.02) block repeated
       block = rounded(np.random.default_rng(seed), (1024, 1024), 0.02, True)
       return np.tile(block, (-(-rows // 1024), -(-cols // 1024)))[:rows, :cols]
     def shard(rows, cols, seed, fmt): return Tensor.frombytes(rt, rows, cols, np.ascontiguousarray(tiled(rows, cols, seed)).tobytes()).cast(fmt).columns()
     K3, N3, V4 = 8192, 28672, 128256
     a, b = bd.split_tiles(N3, world, rank)
-    mlp = bd.ShardedMLP(rt, shard(K3, b - a, 1, "bfp4"), shard(K3, b - a, 2, "bfp4"), shard(b - a, K3, 3, "bfp4"))
+    mlp = bd.ShardedMLP(rt, shard(K3, b - a, 1, "bfp4"), shard(K3, b - a, 2, "bfp4"), shard(b - a, K3, 3, "bfp4"), comm)
     va, vb = bd.split_tiles(V4, world, rank)
-    head = bd.ShardedHead(rt, shard(K3, vb - va, 4, "bfp8"), va)
-    sharded = {"mlp": [], "head": []}
+    head = bd.ShardedHead(rt, shard(K3, vb - va, 4, "bfp8"), va, comm)
+    mlp_bytes, head_bytes = 3 * (K3 // 32) * (N3 // 32) * TILE["bfp4"], (K3 // 32) * (V4 // 32) * TILE["bfp8"]
+    sharded = {"ranks": world, "mlp": [], "head": [],
+               "mlp_ideal_us": round(mlp_bytes / world / peak / 1e3, 1), "head_ideal_us": round(head_bytes / world / peak / 1e3, 1)}
+    def median_us(fn):
+      for _ in range(5): fn()
+      return round(statistics.median(timed(fn, 10) / 10 for _ in range(4)) * 1e3, 1)   # a median: the first collective of a size may set up connections
     for m in (1, 4, 16):
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
       for gather in (True, False):
-        fn = lambda: mlp.forward(xs, gather=gather)
-        for _ in range(5): fn()
-        ms_ = statistics.median(timed(fn, 5) / 5 for _ in range(4))      # a median: the first collective of a size may set up connections
-        total = 3 * (K3 // 32) * (N3 // 32) * TILE["bfp4"]
-        sharded["mlp"].append({"M": m, "all_gather": gather, "us": round(ms_ * 1e3, 1), "GBps_all_ranks": round(total / (ms_ * 1e-3) / 1e9, 1)})
+        us = median_us(lambda: mlp.forward(xs, gather=gather))
+        sharded["mlp"].append({"M": m, "all_gather": gather, "us": us, "GBps_all_ranks": round(mlp_bytes / us / 1e3, 1)})
     for m in (1, 4, 8):
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
-      fn = lambda: head.pick(xs)
-      for _ in range(5): fn()
-      ms_ = statistics.median(timed(fn, 5) / 5 for _ in range(4))
-      total = (K3 // 32) * (V4 // 32) * TILE["bfp8"]
-      sharded["head"].append({"M": m, "us": round(ms_ * 1e3, 1), "GBps_all_ranks": round(total / (ms_ * 1e-3) / 1e9, 1)})
-    sharded["note"] = ("configs[3]: gate/up [8192,28672] bfp4 split over N, down [28672,8192] split over K, all-reduce of fp32 partials, with or "
-                       "without the all-gather between them; configs[4]: LM head [8192,128256] bfp8 split over the vocabulary, fused argmax, "
-                       "pairs gathered over NCCL; times are the max over ranks, bytes are the packed weights of all ranks")
+      us = median_us(lambda: head.pick(xs))
+      sharded["head"].append({"M": m, "us": us, "GBps_all_ranks": round(head_bytes / us / 1e3, 1)})
+    sharded["note"] = ("configs[3]: gate/up [8192,28672] bfp4 split over N, down [28672,8192] split over K: one queue launch, an all-reduce of "
+                       "fp32 partial sums and a rounding kernel, with or without the all-gather of the gate/up result; configs[4]: LM head "
+                       "[8192,128256] bfp8 split over the vocabulary: fused pick, all-gather of 256 bytes per rank, combining kernel")
+    rt.wait()
+    comm.close()
 
   if dist is not None: dist.barrier()
   if rank == 0:

@@ -29,6 +29,7 @@ extern "C" {
 
 enum { BT_OK = 0, BT_BAD_ARGUMENT = 1, BT_DEVICE = 2, BT_TIMEOUT = 3, BT_NO_MEMORY = 4 };
 enum { BT_BF16 = 0, BT_FP32 = 1, BT_INT32 = 2, BT_BFP8 = 8, BT_BFP4 = 4 };            /* storage formats */
+enum { BT_FP32_ROWS = 16 };   /* a matmul result as fp32 ROW-MAJOR [M, N] instead of tiles (only rows < M are written) */
 enum { BT_EPI_NONE = 0, BT_EPI_RELU = 1, BT_EPI_SILU = 2, BT_EPI_GLU = 3, BT_EPI_ARGMAX = 4 };
 
 typedef struct bt_device_info {
@@ -102,7 +103,8 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
  *          out = silu(x @ w) * (x @ w2) (baretile/models/llama.py:179-183).
  *   add    0, or bf16 tiles of an (M or 1) x N addend, added before the activation
  *          (baretile/kernels.py:593-599).
- *   out    bf16 or fp32 tiles (out_dtype), rows past M zero; or with BT_EPI_ARGMAX nothing, and
+ *   out    bf16 or fp32 tiles (out_dtype), rows past M zero (or, with BT_FP32_ROWS, fp32 row-major [M, N]: the form
+ *          an all-reduce of partial sums wants); or with BT_EPI_ARGMAX nothing, and
  *          arg_val[M] (fp32) / arg_idx[M] (int32) receive each row's largest value and its first
  *          column (topk_kernel's tie rule, baretile/kernels.py:1173-1231), index + arg_base.
  *   work   scratch of at least bt_gemv_workspace_bytes() bytes, zeroed once before first use;
@@ -156,7 +158,7 @@ int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
  * Some embedders of this library run where cudaMalloc is off limits -- inside another framework's capture or
  * allocator-owned region, in a process whose memory budget was handed out in full at start-up, or in a plug-in
  * that is only ever given its input and output buffers. For them the scratch that bt_gemv_bfp takes from the
- * caller sits in a fixed array inside the library's device image (about 3.7 MB on every GPU that loads the
+ * caller sits in a fixed array inside the library's device image (about 0.7 MB on every GPU that loads the
  * library, held until the process exits). The call allocates and frees nothing, on the host side either.
  * Limits, rejected with BT_BAD_ARGUMENT: M <= 8 rows of x, N <= 524288 columns. Inputs and outputs are the
  * caller's, exactly as for bt_gemv_bfp. The first call on a device looks the array's address up (one runtime
@@ -172,6 +174,29 @@ int bt_gemv_bfp_static(int device, int fmt, int epilogue, int M, int K, int N, u
  * stream; if the flag was set, clears it and the counters that launch may have left half-counted. work = 0 asks
  * about the built-in scratch of bt_gemv_bfp_static on that device. */
 int bt_gemv_check(int device, uint64_t work, uint64_t stream, int *error);
+/* ---- exchanges between the GPUs of one box, for layers split over them ----
+ * The reference has no collectives; its transport between chips is the point-to-point copy of Tensor.to
+ * (baretile/tensor.py:708-726) over link_kernel (baretile/kernels.py:1316-1372). These entry points carry what the
+ * split layers of this path need instead, as NCCL collectives queued on the caller's stream (NCCL is loaded on first
+ * use; a process that never calls them needs none).
+ *   bt_comm_unique_id   128 bytes that one rank makes and hands to the others by any means.
+ *   bt_comm_init        every rank, with its device current: joins the communicator of `world` ranks.
+ *   bt_allgather        `bytes` from every rank into dst, ranks one after another. On bf16 tile buffers of [M, N/world]
+ *                       column slices this yields the [M, N] tensor in tile layout as it is (gate/up split over N).
+ *   bt_allreduce_sum    in-place sum of `count` fp32 over the ranks (down projection split over K: BT_FP32_ROWS partial
+ *                       sums), then bt_round_tilize rounds [rows, cols] fp32 row-major to bf16 tiles of one tile row,
+ *                       half up like every matmul result.
+ *   bt_argmax_combine   the greedy pick over a vocabulary split across ranks: `blocks` holds, per rank, 32 fp32
+ *                       values then 32 int32 global indices (a matmul's pick with arg_idx = arg_val + 128 bytes,
+ *                       gathered by bt_allgather of 256 bytes); per row the larger value wins, of equal values the
+ *                       lower index (topk_kernel's tie rule, baretile/kernels.py:1228-1231). */
+int bt_comm_unique_id(void *id, size_t bytes);
+int bt_comm_init(int device, int rank, int world, const void *id, uint64_t *comm);
+int bt_comm_destroy(uint64_t comm);
+int bt_allgather(int device, uint64_t comm, uint64_t src, uint64_t dst, size_t bytes, uint64_t stream);
+int bt_allreduce_sum(int device, uint64_t comm, uint64_t buf_f32, size_t count, uint64_t stream);
+int bt_round_tilize(int device, uint64_t src_f32_rows, uint64_t dst_bf16_tiles, int rows, int cols, uint64_t stream);
+int bt_argmax_combine(int device, uint64_t blocks, int world, int rows, uint64_t out_val, uint64_t out_idx, uint64_t stream);
 /* Number of GPU kernels this library has launched on behalf of the calling process. */
 int bt_launch_count(uint64_t *count);
 

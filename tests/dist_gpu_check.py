@@ -2,7 +2,6 @@
 checked on every rank against the oracle's unsharded fp32 NumPy result. Prints one 'ok' line per rank."""
 import os, sys
 import numpy as np
-import torch
 import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -17,9 +16,9 @@ def main():
   from baretile_b200.chip import Chip
   from baretile_b200.runtime import Runtime
   rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
-  torch.cuda.set_device(local)
-  dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+  dist.init_process_group("gloo")                                   # only hands the communicator's id round
   rt = Runtime(Chip(pci.open_device(local)))
+  comm = bd.Comm(rt, rank, world)
   rng = np.random.default_rng(42)                                   # the same inputs on every rank
   k, n, vocab = 1024, 2048 * world // 2 if world > 2 else 2048, 4096 * max(1, world // 2)
   for m in (1, 4, 16):
@@ -28,31 +27,34 @@ def main():
     a, b = bd.split_tiles(n, world, rank)
     tx = upload(rt, x)
     mlp = bd.ShardedMLP(rt, upload(rt, wg[:, a:b]).cast("bfp4").columns(), upload(rt, wu[:, a:b]).cast("bfp4").columns(),
-                        upload(rt, wd[a:b]).cast("bfp4").columns())
+                        upload(rt, wd[a:b]).cast("bfp4").columns(), comm)
     h = o.bf16_floats(o.bf16_half_up(o.matmul(x, o.dequant(wg, "bfp4"), "glu", o.dequant(wu, "bfp4"))))
     want = o.matmul(h, o.dequant(wd, "bfp4"))
     for gather in (True, False):
       got = mlp.forward(tx, gather=gather).numpy()
       err = o.rel_err(got, want)
       assert err <= 1e-2, (rank, m, gather, err)
+      if gather:                                                    # the gathered activations are the unsharded ones
+        full = mlp.gathered.numpy()[:m]
+        assert o.rel_err(full, h) <= 1e-2, (rank, m, o.rel_err(full, h))
     # LM head: vocabulary split, index-exact against the unsharded fp32 logits of the same kernels' arithmetic
     wv = weights(rng, k, vocab)
     wv[:, 5] = wv[:, vocab - 7]                                     # equal columns on the first and the last rank: a tie
     va, vb = bd.split_tiles(vocab, world, rank)
-    head = bd.ShardedHead(rt, upload(rt, wv[:, va:vb]).cast("bfp8").columns(), va)
-    vals, ids = head.pick(tx)
-    rt.wait()
+    head = bd.ShardedHead(rt, upload(rt, wv[:, va:vb]).cast("bfp8").columns(), va, comm)
+    head.pick(tx)
+    vals, got_ids = head.read(m)
     logits = x.astype(np.float32) @ o.dequant(wv, "bfp8")
     ref = o.argmax(logits)
     gap = np.sort(logits, -1)[:, -1] - np.sort(logits, -1)[:, -2]
     near = (gap <= 2.0 ** -8 * (np.abs(x) @ np.abs(o.dequant(wv, "bfp8"))).max(-1)) & (gap > 0)
-    got_ids = ids.cpu().numpy()
     assert np.array_equal(got_ids[~near], ref[~near]), (rank, m, got_ids, ref)
-    assert o.rel_err(vals.cpu().numpy(), logits.max(-1)) < 1e-3
+    assert o.rel_err(vals, logits.max(-1)) < 1e-3
   rt.wait()
   every = [None] * world
   dist.all_gather_object(every, "ok")
   print(f"rank {rank} of {world}: ok", flush=True)
+  comm.close()
   rt.close()
   dist.destroy_process_group()
 

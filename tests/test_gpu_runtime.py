@@ -121,7 +121,7 @@ def test_bounded_device_wait_reports_instead_of_hanging(rt):
   # Runtime.wait turns into RuntimeError; the kernel ends normally and the runtime keeps working. The wait is made
   # unmeetable on the host: the arrival counters of the matrix' sub-panels in the scratch start far below zero, so
   # a sub-panel's owner never sees its contributors arrive. Offsets: the first scratch set starts at byte 256 of the
-  # workspace and its counters (one int per sub-panel of 4 tile columns) 256 bytes further (kWsSets, kSetCounters in
+  # workspace and its counters (one int per sub-panel of 4 tile columns) 512 bytes further (kWsSets, kSetCounters in
   # csrc/gemv.cu).
   from helpers import acts, upload, weights
   from oracle import bfp_oracle as o
@@ -130,7 +130,7 @@ def test_bounded_device_wait_reports_instead_of_hanging(rt):
   tx, tw = upload(rt, x), upload(rt, w).cast("bfp8").columns()
   good = (tx @ tw).realize().numpy()
   rt.wait()
-  counters = rt.work + 256 + 256
+  counters = rt.work + 256 + 512
   poisoned = (ctypes.c_int * 4)(*([-1000] * 4))
   rt.upload(counters, bytes(poisoned))
   y = (tx @ tw).realize()
