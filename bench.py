@@ -179,6 +179,11 @@ def main():
   from baretile_b200.runtime import Runtime
   from baretile_b200.tensor import Tensor
   dist = None
+  # stdout carries the one JSON line and nothing else: whatever libraries print there meanwhile (NCCL announces its
+  # version when it starts) goes to stderr
+  sys.stdout.flush()
+  json_out = os.fdopen(os.dup(1), "w")
+  os.dup2(2, 1)
   if world > 1:
     import torch, torch.distributed as dist
     torch.cuda.set_device(local)
@@ -454,13 +459,7 @@ def main():
   sharded = None
   if dist is not None:
     from baretile_b200 import dist as bd
-    sys.stdout.flush()
-    keep = os.dup(1)
-    os.dup2(2, 1)                     # NCCL may announce its version on stdout, which carries the one JSON line
-    try: comm = bd.Comm(rt, rank, world)
-    finally:
-      os.dup2(keep, 1)
-      os.close(keep)
+    comm = bd.Comm(rt, rank, world)
     def tiled(rows, cols, seed):      # bf16 bits of a rows x cols matrix, a 1024 x 1024 N(0, 0.02) block repeated
       block = rounded(np.random.default_rng(seed), (1024, 1024), 0.02, True)
       return np.tile(block, (-(-rows // 1024), -(-cols // 1024)))[:rows, :cols]
@@ -514,7 +513,8 @@ def main():
     if not args.no_cpu:
       v, dt, sample, detail = cpu_sample(args.reference)
       line["cpu_baseline"] = {"value": round(v, 3), "unit": "GB/s", "cores": os.cpu_count(), "kind": detail["kind"], "sample": sample, "detail": detail}
-    print(json.dumps(line))
+    json_out.write(json.dumps(line) + "\n")
+    json_out.flush()
   rt.close()
   if dist is not None: dist.destroy_process_group()
 
