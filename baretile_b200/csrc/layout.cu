@@ -66,12 +66,10 @@ __global__ void round_bf16_kernel(const uint32_t *__restrict__ src, uint16_t *__
 // One thread packs one run: the 16 datums of a face row share their largest exponent field.
 // bfp8: q = min((m + (1 << s)) >> (s + 1), 127) with s = min(top - e, 8); byte = q ? sign << 7 | q : 0.
 // bfp4: q = s < 4 ? min((m + (16 << s)) >> (s + 5), 7) : 0; nibble = q ? sign << 3 | q : 0, even datum low.
+// Packs the run in w (16 bf16 values, two to a word) into `values` (16 bytes for bfp8, the first 8 for bfp4) and
+// returns the shared exponent.
 template <int FMT>
-__global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__ dst, size_t runs) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= runs) return;
-  uint4 lo = src[2 * i], hi = src[2 * i + 1];
-  uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+__device__ __forceinline__ uint32_t pack_run(const uint32_t (&w)[8], uint32_t (&values)[4]) {
   uint32_t top = 0;
 #pragma unroll
   for (int k = 0; k < 8; k++) top = max(top, max(w[k] >> 7 & 255u, w[k] >> 23 & 255u));
@@ -87,22 +85,82 @@ __global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__
       q[k] = v ? (b >> 15) << 3 | v : 0u;
     }
   }
+  if (FMT == BT_BFP8) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) values[i] = q[4 * i] | q[4 * i + 1] << 8 | q[4 * i + 2] << 16 | q[4 * i + 3] << 24;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+      values[i] = q[8 * i] | q[8 * i + 1] << 4 | q[8 * i + 2] << 8 | q[8 * i + 3] << 12 | q[8 * i + 4] << 16 | q[8 * i + 5] << 20 | q[8 * i + 6] << 24 | q[8 * i + 7] << 28;
+    values[2] = values[3] = 0;
+  }
+  return top;
+}
+
+template <int FMT>
+__global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__ dst, size_t runs) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= runs) return;
+  uint4 lo = src[2 * i], hi = src[2 * i + 1];
+  const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  uint32_t v[4];
+  const uint32_t top = pack_run<FMT>(w, v);
   constexpr size_t TB = tile_bytes(FMT);
   uint8_t *tile = dst + i / 64 * TB;
   int r = (int)(i % 64);
   tile[r] = (uint8_t)top;
-  if (FMT == BT_BFP8) {
-    uint4 o;
-    o.x = q[0] | q[1] << 8 | q[2] << 16 | q[3] << 24;
-    o.y = q[4] | q[5] << 8 | q[6] << 16 | q[7] << 24;
-    o.z = q[8] | q[9] << 8 | q[10] << 16 | q[11] << 24;
-    o.w = q[12] | q[13] << 8 | q[14] << 16 | q[15] << 24;
-    *reinterpret_cast<uint4 *>(tile + 64 + r * 16) = o;
+  if (FMT == BT_BFP8) *reinterpret_cast<uint4 *>(tile + 64 + r * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+  else *reinterpret_cast<uint2 *>(tile + 64 + r * 8) = make_uint2(v[0], v[1]);
+}
+
+// ---- put: rows of x into rows of a tensor, in place (the packer's other user: a block-float KV cache) ----------
+// One thread moves one run: the 16 datums of row i of x in one face of one tile column, to row ids[i] of the
+// destination. Into a block float the run is packed exactly as a cast packs it. A row whose place is past the
+// destination's last tile row is skipped; when several rows of x go to the same place the last one wins, so a
+// thread whose place comes up again later in ids leaves its run alone. Distinct rows touch distinct bytes (a run's
+// exponent, its values), so nothing is read back or merged. A destination of one logical row keeps that row in all
+// 32 rows of its tile, so there every place inside the tile writes all 32 (and the last such row of x wins).
+// ids is an int32 row in tile layout: place i is datum (0, i % 32) of tile i / 32.
+template <int FMT>   // BT_BFP8, BT_BFP4, or an item size in bytes (2, 4 coded as -2, -4) for a plain copy
+__global__ void put_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ x, const int *__restrict__ ids, int batch, int n, int tc,
+                           int dst_tr, int x_tr, int single) {
+  const size_t unit = (size_t)blockIdx.x * blockDim.x + threadIdx.x;          // ((b * n + i) * tc + j) * 2 + f
+  if (unit >= (size_t)batch * n * tc * 2) return;
+  const int f = (int)(unit % 2), j = (int)(unit / 2 % tc), i = (int)(unit / 2 / tc % n), b = (int)(unit / 2 / tc / n);
+  auto place = [&](int r) { return ids[(size_t)(r / 32) * 1024 + (r % 32 / 16) * 256 + r % 16]; };
+  const int p = place(i);
+  if (p < 0 || p / 32 >= dst_tr) return;
+  for (int later = i + 1; later < n; later++) {
+    const int q = place(later);
+    if (single ? (unsigned)q < 32u : q == p) return;
+  }
+  constexpr int ITEM = FMT < 0 ? -FMT : 2;                                    // bytes of a datum of x
+  const size_t at_x = (size_t)((i % 32 / 16) * 2 + f) * 256 + (i % 16) * 16;  // first datum of the run in x's tile
+  const uint8_t *src = x + (((size_t)b * x_tr + i / 32) * tc + j) * (1024 * ITEM) + at_x * ITEM;
+  const size_t tile = ((size_t)b * dst_tr + p / 32) * tc + j;
+  constexpr int BFP = FMT < 0 ? BT_BFP8 : FMT, TB = tile_bytes(BFP);
+  uint4 raw[4];
+  uint32_t v[4], top = 0;
+  if (FMT < 0) {
+#pragma unroll
+    for (int k = 0; k < ITEM; k++) raw[k] = reinterpret_cast<const uint4 *>(src)[k];
   } else {
-    uint2 o;
-    o.x = q[0] | q[1] << 4 | q[2] << 8 | q[3] << 12 | q[4] << 16 | q[5] << 20 | q[6] << 24 | q[7] << 28;
-    o.y = q[8] | q[9] << 4 | q[10] << 8 | q[11] << 12 | q[12] << 16 | q[13] << 20 | q[14] << 24 | q[15] << 28;
-    *reinterpret_cast<uint2 *>(tile + 64 + r * 8) = o;
+    const uint4 lo = reinterpret_cast<const uint4 *>(src)[0], hi = reinterpret_cast<const uint4 *>(src)[1];
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    top = pack_run<BFP>(w, v);
+  }
+  for (int r = single ? 0 : p % 32, end = single ? 32 : r + 1; r < end; r++) {
+    const int run = ((r / 16) * 2 + f) * 16 + r % 16;                         // which of the destination tile's 64 runs
+    if (FMT < 0) {
+      uint4 *to = reinterpret_cast<uint4 *>(dst + tile * (1024 * ITEM) + (size_t)run * 16 * ITEM);
+#pragma unroll
+      for (int k = 0; k < ITEM; k++) to[k] = raw[k];
+    } else {
+      uint8_t *t = dst + tile * TB;
+      t[run] = (uint8_t)top;
+      if (BFP == BT_BFP8) *reinterpret_cast<uint4 *>(t + 64 + run * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+      else *reinterpret_cast<uint2 *>(t + 64 + run * 8) = make_uint2(v[0], v[1]);
+    }
   }
 }
 
@@ -241,6 +299,26 @@ int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles
   if (fmt == BT_BFP8) unpack_kernel<BT_BFP8><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint8_t>(src), as_ptr<uint4>(dst), runs);
   else unpack_kernel<BT_BFP4><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint8_t>(src), as_ptr<uint4>(dst), runs);
   return launched("unpack_kernel");
+}
+
+int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batch, int n, int dst_rows, int cols, uint64_t stream) {
+  BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4 || fmt == BT_BF16 || fmt == BT_FP32 || fmt == BT_INT32, "bt_put: unknown format %d", fmt);
+  BT_REQUIRE(dst && x && ids && dst != x && dst != ids && dst % 16 == 0 && x % 16 == 0, "bt_put: needs 16-byte aligned tensors, x and ids apart from dst");
+  if (int s = check_shape("bt_put", batch, n, cols)) return s;
+  BT_REQUIRE(dst_rows > 0, "bt_put: the destination has no rows");
+  if (int s = use_device(device)) return s;
+  const int tc = (cols + 31) / 32, dst_tr = (dst_rows + 31) / 32, x_tr = (n + 31) / 32;
+  const size_t units = (size_t)batch * n * tc * 2;
+  const unsigned blocks = blocks_for(units);
+  uint8_t *d = as_ptr<uint8_t>(dst);
+  const uint8_t *s8 = as_ptr<uint8_t>(x);
+  const int *places = as_ptr<int>(ids);
+  cudaStream_t st = as_stream(stream);
+  if (fmt == BT_BFP8) put_kernel<BT_BFP8><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
+  else if (fmt == BT_BFP4) put_kernel<BT_BFP4><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
+  else if (fmt == BT_BF16) put_kernel<-2><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
+  else put_kernel<-4><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
+  return launched("put_kernel");
 }
 
 int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols, uint64_t src, uint64_t dst, uint64_t stream) {

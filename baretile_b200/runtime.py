@@ -15,11 +15,20 @@ TIMES = 1024           # launches whose timing records are kept (baretile/runtim
 
 
 class Bound(int):
-  """A launch argument a replay can replace (baretile/runtime.py:476-482). Kept for interface parity."""
-  def __new__(cls, value, key):
+  """A launch argument that a replay can replace, such as the address of a jit input; key names it in a binding
+  (baretile/runtime.py:476-482). Adding a byte offset keeps it bound: a replay then points that far into the new
+  allocation."""
+  def __new__(cls, value, key, offset=0):
     self = super().__new__(cls, value)
-    self.key = key
+    self.key, self.offset = key, offset
     return self
+  def __add__(self, other):
+    if isinstance(other, int) and not isinstance(other, Bound): return Bound(int(self) + other, self.key, self.offset + other)
+    return int(self) + int(other)
+  __radd__ = __add__
+  def rebind(self, binding):
+    """The argument's value under `binding` (key -> address); its recorded value when the key is missing."""
+    return binding[self.key] + self.offset if self.key in binding else int(self)
 
 
 def _merge_holes(holes, starts=()):
@@ -41,10 +50,10 @@ class Recording:
   (a temporary of a launch: staging for an upload, the flat scratch of a pick) is used by every replay, so the
   recording keeps it out of the allocator until close().
 
-      with rt.record() as step: y = (x @ w).relu().realize()
-      step.replay()
+      with rt.record() as step: y = (x @ w).relu().realize()      # runs once, like any launches
+      step.replay()                                                # and again
   """
-  def __init__(self, rt): self.rt, self.graph, self.count, self.held = rt, None, 0, []
+  def __init__(self, rt): self.rt, self.graph, self.count, self.held, self.launches = rt, None, 0, [], None
   def __enter__(self):
     self.rt.check()
     if self.rt.recording is not None: raise RuntimeError("a recording is already in progress on this runtime")
@@ -53,6 +62,7 @@ class Recording:
     _lib.call("bt_graph_begin", self.rt.device, self.rt.stream)
     self.outer, self.rt.pending = self.rt.pending, []
     self.rt.recording = self
+    self.outer_log, self.rt.log = self.rt.log, []          # what is launched meanwhile, for replays with a binding
     return self
   def __exit__(self, kind, *_):
     graph = ctypes.c_uint64()
@@ -60,17 +70,33 @@ class Recording:
       try:
         if kind is None: self.rt.flush()
       finally:
+        self.launches, self.rt.log = self.rt.log, self.outer_log
+        if self.outer_log is not None: self.outer_log.extend(self.launches)
         self.rt.pending, self.rt.recording = self.outer, None
         _lib.call("bt_graph_end", self.rt.device, self.rt.stream, ctypes.byref(graph))
     except Exception:
       if kind is None: raise
       return
     self.graph, self.count = graph.value, self.rt.launches - self.first
-  def replay(self):
+    # what was recorded also runs once, as it would have without the recording (the reference's Recording logs launches
+    # that execute as usual): the results exist when the block ends
+    _lib.call("bt_graph_launch", self.rt.device, self.graph, self.rt.stream)
+  def replay(self, binding=None):
+    """Queue the recorded launches again. Without a binding they replay as recorded, with one call. `binding` maps
+    a Bound argument's key to its value for this replay (an argument whose key is missing keeps its recorded value,
+    baretile/tensor.py:1194-1214): the launches are then queued again one by one with the new values, the matmuls
+    among them still leaving as one queue launch."""
     self.rt.check()
     if self.graph is None: raise RuntimeError("nothing was recorded")
-    _lib.call("bt_graph_launch", self.rt.device, self.graph, self.rt.stream)
-    self.rt.launches += self.count
+    if self.rt.recording is not None: raise RuntimeError("cannot replay while recording on the same runtime")
+    if not binding:
+      _lib.call("bt_graph_launch", self.rt.device, self.graph, self.rt.stream)
+      self.rt.launches += self.count
+      return
+    with self.rt.queue():
+      for kernel, args, units, name in self.launches:
+        self.rt.launch(kernel, tuple(a.rebind(binding) if isinstance(a, Bound) else a for a in args), units, name)
+  send = replay                          # the reference's name for it
   def close(self):
     """Drop the recording and hand the memory it kept back to the allocator."""
     if self.graph is not None and self.rt.active: _lib.lib().bt_graph_destroy(self.rt.device, self.graph)

@@ -182,6 +182,33 @@ class Tensor:
     self._relayout(x.addr, out.addr, to_stream=1)
     return out
 
+  def put(self, ids, x):
+    """Write x into the rows selected by ids, in place: how models update KV caches without changing the shape of a
+    decode step (baretile/tensor.py:224-241). For a block-float destination x is bf16 and is rounded as in cast."""
+    self._same_runtime(ids, x)
+    if not (ids.dtype == "int32" and ids.shape[:2] == (1, 1) and ids.cols == x.rows):
+      raise ValueError("put needs ids as an int32 row, with one position for each row of x")
+    if not ((x.batch, x.cols) == (self.batch, self.cols) and x.dtype == ("bf16" if self.dtype in BFP else self.dtype)):
+      raise ValueError(f"put needs rows of the cache's batch and width, "
+                       f"bf16 for a block float: {x.shape} {x.dtype} into {self.shape} {self.dtype}")
+    if self.runs: raise ValueError("put writes a tensor in tile order, not one laid out by columns")
+    x, ids = x.realize(), ids.realize()
+    if 2 * x.rows + self.tr > 2**17: raise ValueError("put has too many rows")   # the reference's bound, kept
+    self.realize()
+    self._stream = None                     # a copy by columns made earlier no longer matches
+    held = []                               # x or ids that is the tensor itself is copied first, as the reference does
+    def apart(t):
+      if t.addr != self.addr: return t.addr
+      size = t.tiles * tile_bytes(t.dtype)
+      held.append(self.rt.dram_alloc(size))
+      self.rt.launch("bt_d2d", (held[-1], t.addr, size), name="copy")
+      return held[-1]
+    try:
+      self.rt.launch("bt_put", (FMT_CODE[self.dtype], self.addr, apart(x), apart(ids), self.batch, x.rows, self.rows, self.cols), name="put")
+    finally:
+      for a in held: self.rt.dram_free(a)
+    return self
+
   def float(self): return self.cast("fp32")
   def bfloat16(self): return self.cast("bf16")
 
@@ -248,6 +275,46 @@ class Tensor:
     _launch_matmul(self.rt, e, epilogue, self, self.rows)
     self.op, self.srcs = None, ()
     return self
+
+
+# ---- jit ----------------------------------------------------------------------------------------------------------
+
+def jit(f):
+  """Run f normally on the first call, record the second call's launches, then replay them: later calls queue the
+  same launches with the new inputs' addresses and skip f's Python code (baretile/tensor.py:1220-1293). Inputs are
+  realized tensors whose shapes and dtypes stay fixed; the result reuses its buffer, so the next call overwrites it.
+  f must not read tensors back to the host."""
+  import functools
+  from baretile_b200.runtime import Bound
+  signature, rec, out = None, None, None
+  @functools.wraps(f)
+  def run(*xs):
+    nonlocal signature, rec, out
+    if not xs or not all(isinstance(x, Tensor) for x in xs): raise ValueError("jit inputs must be tensors, with at least one input")
+    rt = xs[0].rt
+    if any(x.rt is not rt for x in xs): raise ValueError("jit inputs must use the same runtime")
+    if signature is None:
+      result = f(*xs).realize()
+      signature = [(x.rt, x.shape, x.dtype, x.runs) for x in xs]
+      return result
+    if len(xs) != len(signature): raise ValueError(f"jit expected {len(signature)} inputs, got {len(xs)}")
+    for x, (runtime, shape, dtype, runs) in zip(xs, signature):
+      if x.rt is not runtime: raise ValueError("jit inputs must use the recorded runtime")
+      if (x.shape, x.dtype) != (shape, dtype): raise ValueError(f"a jit input is {x.shape} {x.dtype}, where the first call had {shape} {dtype}")
+      if x.runs != runs: raise ValueError("a jit input by columns must keep the layout it was recorded with")
+    xs = [x.realize() for x in xs]
+    if rec is None:
+      ins = []
+      for i, x in enumerate(xs):       # stand-ins at the inputs' places, under addresses bound to their positions
+        t = Tensor.__new__(Tensor)
+        t.__dict__.update(x.__dict__)
+        t.addr, t.owner, t._stream = Bound(x.addr, i), x, None
+        ins.append(t)
+      with rt.record() as rec: out = f(*ins).realize()
+      return out
+    rec.replay({i: x.addr for i, x in enumerate(xs)})
+    return out
+  return run
 
 
 # ---- expression matching -------------------------------------------------------------------------------------------

@@ -89,6 +89,15 @@ int bt_round_bf16(int device, uint64_t src_f32, uint64_t dst_bf16, size_t count,
 int bt_pack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, uint64_t stream);
 int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, uint64_t stream);
 
+/* Tensor.put / put_kernel (baretile/tensor.py:224-241, baretile/kernels.py:1083-1168): rows of x written in place into
+ * the rows of dst that ids names, e.g. new keys and values into a KV cache. dst: batch matrices of dst_rows x cols in
+ * tile layout, format fmt. x: batch matrices of n x cols, bf16 when dst is a block float (each run of 16 is then
+ * rounded exactly as bt_pack_bfp rounds it), else dst's format. ids: an int32 row of n places in tile layout. A
+ * place past dst's last tile row is skipped (one in the padding of the last tile row is written there); of several
+ * rows to one place the last wins. A dst of one row keeps it in all 32 rows of its tile, as every one-row tensor
+ * does. x and ids must not overlap dst: the caller copies an aliased one first (Tensor.put does). */
+int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batch, int n, int dst_rows, int cols, uint64_t stream);
+
 /* Tensor.columns() / columns_kernel (baretile/tensor.py:598-611, baretile/kernels.py:1455-1481): a pure
  * byte permutation of a (tile_rows x tile_cols) block-float matrix into the layout the matmul streams.
  * Runs of 4 tile columns; inside a run, tile row by tile row; inside a tile, exponents then values,

@@ -1,7 +1,7 @@
 """CPU oracle for the block-float matmul path. TEST INFRASTRUCTURE ONLY.
 
 This is a NumPy restatement of the reference's algorithms for tile layout, bfp8/bfp4 packing and
-unpacking, the fp32 matmul with its epilogues and the stable argmax. Only tests, the smoke check
+unpacking, rows put in place into a cache, the fp32 matmul with its epilogues and the stable argmax. Only tests, the smoke check
 and the benchmark's CPU-baseline leg import it; the product (baretile_b200) never does.
 
 Parity pin: every function here is checked against outputs of the reference's own Python code
@@ -141,6 +141,41 @@ def unpack_tiles(tiles, dtype):
   shift = 8 - bl
   out = (x >> 7) << 15 | ((e - shift) % 256) << 7 | ((m << np.maximum(shift, 0)) & 0x7E)
   return np.where(mag == 0, np.where(x >> 7 != 0, 0xFF80, 0), out).astype(np.uint16)
+
+
+# ---- put: rows written in place, the way a KV cache takes them --------------------------------------
+
+def put(dst_tiles, places, x_tiles, dtype, batch, dst_rows):
+  """Rows of x into the rows of a tensor that `places` names, on storage bytes; returns the new tiles.
+
+  dst_tiles: (batch * tr * tc, tile_bytes(dtype)) uint8. x_tiles: (batch * xr * tc, tile_bytes(xd)) uint8 with
+  xd = bf16 when dtype is a block float, else dtype. places: n ints, one for each row of x.
+  Follows put_kernel (baretile/kernels.py:1083-1168): rows go first to last, so a later row to the same place
+  wins (:1097-1098); a place whose tile row is past the tensor's last is skipped, one in the padding of the last
+  tile row is written there (:1099-1100, the test `place / 32 < tr` at :1147 on unsigned places, so a negative
+  place is skipped too); a row is two runs of 16, the left and right face of each tile column (:1107-1111);
+  into a block float a run is packed as a cast packs it: its exponent byte, then its values (:1126-1135); a
+  tensor of one logical row takes the row into all 32 rows of its tile (:1111, `a[15] == 1`)."""
+  bfp = dtype in BFP
+  item = 2 if bfp else ITEMSIZE[dtype]
+  n = len(places)
+  dst = np.array(dst_tiles, np.uint8)
+  tr, xr = -(-dst_rows // 32), -(-n // 32)
+  tc = dst.shape[0] // (batch * tr)
+  dst = dst.reshape(batch, tr, tc, -1)
+  x = np.asarray(x_tiles, np.uint8).reshape(batch * xr * tc, -1)
+  if bfp: x = pack_tiles(x.view(np.uint16), dtype)     # runs pack independently, so a tile packs run by run
+  x = x.reshape(batch, xr, tc, -1)
+  per = BFP[dtype] // 64 if bfp else 16 * item           # value bytes of a run
+  first = 64 if bfp else 0
+  for i, p in enumerate(int(p) & 0xFFFFFFFF for p in places):
+    if p // 32 >= tr: continue
+    for r in (range(32) if dst_rows == 1 else (p % 32,)):
+      for f in range(2):
+        a, b = at(i % 32, 16 * f) // 16, at(r, 16 * f) // 16   # the run in x's tile, in the tensor's tile
+        if bfp: dst[:, p // 32, :, b] = x[:, i // 32, :, a]
+        dst[:, p // 32, :, first + b * per:first + (b + 1) * per] = x[:, i // 32, :, first + a * per:first + (a + 1) * per]
+  return dst.reshape(batch * tr * tc, -1)
 
 
 # ---- streaming layout (the B200 backend's own `columns()` layout) ---------------------------------------

@@ -140,3 +140,41 @@ def test_bounded_device_wait_reports_instead_of_hanging(rt):
   assert np.array_equal(again, good)
   assert o.rel_err(good, x @ o.dequant(w, "bfp8")) <= 1e-2
   del y
+
+
+def test_replay_with_bound_arguments_and_jit(rt):
+  # a recorded chain whose input address is a Bound argument replays on other tensors (baretile/runtime.py:476-482,
+  # baretile/tensor.py:1194-1214), and tensor.jit does the same by itself from its third call on
+  from helpers import acts, upload, weights
+  from baretile_b200.runtime import Bound
+  from baretile_b200.tensor import Tensor, jit
+  rng = np.random.default_rng(55)
+  host = [(weights(rng, 512, 1024) * 2, weights(rng, 512, 1024) * 2, weights(rng, 1024, 512) * 2) for _ in range(2)]
+  layers = [tuple(upload(rt, w).cast("bfp8").columns() for w in ws) for ws in host]
+  head = upload(rt, weights(rng, 512, 1024)).cast("bfp8").columns()
+  def f(x):
+    h = x
+    for wg, wu, wd in layers:
+      a = ((h @ wg).silu() * (h @ wu)).realize()
+      h = (a @ wd).relu().realize()
+    return h
+  xs = [upload(rt, acts(rng, 4, 512)) for _ in range(4)]
+  want = [f(x).numpy() for x in xs]
+  # by hand: record on a stand-in whose address is bound to the key "x", replay on each input
+  stand_in = Tensor.__new__(Tensor)
+  stand_in.__dict__.update(xs[0].__dict__)
+  stand_in.addr, stand_in.owner = Bound(xs[0].addr, "x"), xs[0]
+  with rt.record() as step: out = f(stand_in)
+  assert any(isinstance(a, Bound) for _, args, _, _ in step.launches for a in args)
+  for x, w in zip(xs, want):
+    step.replay({"x": x.addr})
+    rt.wait()
+    assert np.array_equal(out.numpy(), w)
+  step.replay()                                                      # no binding: as recorded, on xs[0]
+  rt.wait()
+  assert np.array_equal(out.numpy(), want[0])
+  step.close()
+  # jit: the first call runs f, the second records, later ones replay with the new input's address
+  fast = jit(f)
+  for x, w in zip(xs, want): assert np.array_equal(fast(x).numpy(), w)
+  with pytest.raises(ValueError, match="where the first call had"): fast(upload(rt, acts(rng, 5, 512)))

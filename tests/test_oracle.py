@@ -98,3 +98,72 @@ def test_matmul_and_argmax():
   assert np.array_equal(o.matmul(x, wd, "relu"), np.maximum(g, 0))
   assert o.argmax(np.array([[1.0, 3.0, 3.0], [-0.0, 0.0, -1.0]])).tolist() == [1, 0]
   assert o.rel_err(g, g) == 0
+
+
+def _tiles_u8(a, dtype):
+  """Row-major values -> storage bytes of a plain (not block-float) tensor, as (tiles, tile_bytes)."""
+  if dtype == "bf16": t = o.tilize(o.bf16_bits(a))
+  else: t = o.tilize(np.asarray(a, np.int32 if dtype == "int32" else np.float32))
+  return t.view(np.uint8).reshape(t.shape[0], -1)
+
+
+def _values(tiles, dtype, batch, rows, cols):
+  """Storage bytes -> row-major values; block floats through the unpacker."""
+  t = np.ascontiguousarray(tiles)
+  if dtype in o.BFP: return o.bf16_floats(o.untilize(o.unpack_tiles(t, dtype), batch, rows, cols))
+  if dtype == "bf16": return o.bf16_floats(o.untilize(t.view(np.uint16), batch, rows, cols))
+  return o.untilize(t.view(np.int32 if dtype == "int32" else np.float32), batch, rows, cols)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp32"])
+def test_put_is_row_assignment_in_order(dtype):
+  """The statement of the reference's own test (test/test_kernels.py:2064-2081): scattered places over several tile
+  rows, one place twice with the later row winning, then a prompt's rows in order into an empty cache."""
+  rng = np.random.default_rng(101)
+  cache, x = (rng.normal(0, 1, s).astype(np.float32) for s in ((3, 200, 96), (3, 70, 96)))
+  if dtype == "bf16": cache, x = o.bf16_floats(o.bf16_bits(cache)), o.bf16_floats(o.bf16_bits(x))
+  places = [int(p) for p in rng.permutation(200)[:70]]
+  places[51] = places[3]
+  got = o.put(_tiles_u8(cache, dtype), places, _tiles_u8(x, dtype), dtype, 3, 200)
+  for i, p in enumerate(places): cache[:, p] = x[:, i]
+  assert np.array_equal(_values(got, dtype, 3, 200, 96), cache)
+  rows = o.bf16_floats(o.bf16_bits(rng.normal(0, 1, (3, 40, 64))))
+  got = _values(o.put(_tiles_u8(np.zeros((3, 64, 64)), "bf16"), range(5, 45), _tiles_u8(rows, "bf16"), "bf16", 3, 64), "bf16", 3, 64, 64)
+  assert np.array_equal(got[:, 5:45], rows) and not got[:, :5].any() and not got[:, 45:].any()
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_put_into_a_block_float_rounds_as_cast(fmt):
+  """Rows put into a block-float cache equal the same rows cast, bit for bit (test/test_kernels.py:2106-2122): one
+  row, rows in two tiles, a prompt filling a tile, the edges; and places that are skipped or land in the padding."""
+  rng = np.random.default_rng(102)
+  tiles = o.pack_tiles(o.tilize(np.zeros((4, 96, 64), np.uint16)), fmt)
+  want = np.zeros((4, 96, 64), np.float32)
+  for places in ([7], [35, 36, 71], list(range(32, 64)), [0, 95]):
+    x = o.bf16_floats(o.bf16_bits(rng.normal(0, 2, (4, len(places), 64)) * 10.0 ** rng.integers(-3, 3, (4, len(places), 1))))
+    tiles = o.put(tiles, places, _tiles_u8(x, "bf16"), fmt, 4, 96)
+    want[:, places] = _values(o.pack_tiles(o.tilize(o.bf16_bits(x)), fmt), fmt, 4, len(places), 64)
+    assert np.array_equal(_values(tiles, fmt, 4, 96, 64), want), places
+  # 70 rows: tile row 3 does not exist (skipped, like a negative place); row 75 is padding of the last tile row
+  small = o.pack_tiles(o.tilize(np.zeros((1, 70, 32), np.uint16)), fmt)
+  x = o.bf16_floats(o.bf16_bits(rng.normal(0, 1, (1, 4, 32))))
+  got = o.put(small, [96, -1, 75, 2], _tiles_u8(x, "bf16"), fmt, 1, 70)
+  cast = _values(o.pack_tiles(o.tilize(o.bf16_bits(x)), fmt), fmt, 1, 4, 32)
+  full = _values(got, fmt, 1, 96, 32)
+  assert np.array_equal(full[0, 75], cast[0, 2]) and np.array_equal(full[0, 2], cast[0, 3])
+  assert not np.delete(full[0], [75, 2], axis=0).any()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp32", "int32", "bfp8", "bfp4"])
+def test_put_into_a_single_row_fills_the_tile(dtype):
+  """A tensor of one row holds it in all 32 rows of its tile, and put keeps that. The known answer is the
+  reference's (test/test_kernels.py:2095-2103): [[2, 3]] put into zeros reads back 0x4000, 0x4040 in every row of
+  the left faces of a block float."""
+  xd = "bf16" if dtype in o.BFP else dtype
+  zero = np.zeros((1, o.tile_bytes(dtype)), np.uint8)
+  got = o.put(zero, [0], _tiles_u8(np.array([[[2, 3]]]), xd), dtype, 1, 1)
+  if dtype in o.BFP:
+    rows = o.unpack_tiles(got, dtype).reshape(4, 16, 16)[[0, 2], :, :2]
+    assert np.all(rows == [0x4000, 0x4040])
+  else:
+    assert np.array_equal(_values(got, dtype, 1, 32, 2)[0], np.tile([2, 3], (32, 1)))
