@@ -53,7 +53,7 @@ SIGNATURES = {
   "bt_relayout": [i32, i32, i32, i32, i32, u64, u64, u64],
   "bt_gemv_workspace_bytes": [i32, ctypes.POINTER(size_t)],
   "bt_gemv_bfp": [i32, i32, i32, i32, i32, i32, u64, u64, u64, u64, f32, u64, i32, u64, u64, i32, u64, size_t, u64],
-  "bt_gemm_bfp": [i32, i32, i32, i32, i32, i32, u64, u64, u64, f32, u64, i32, u64, u64],
+  "bt_gemm_bfp": [i32, i32, i32, i32, i32, i32, u64, u64, u64, u64, i32, f32, u64, i32, u64, u64],
   "bt_gemv_bfp_static": [i32, i32, i32, i32, i32, i32, u64, u64, u64, u64, f32, u64, i32, u64, u64, i32, u64],
   "bt_gemv_check": [i32, u64, u64, ctypes.POINTER(i32)],
   "bt_gemv_queue": [i32, i32, ctypes.POINTER(GemvOp), u64, size_t, u64],

@@ -13,7 +13,9 @@ inline unsigned blocks_for(size_t items) { return (unsigned)((items + kThreads -
 // ---- tilize / untilize ------------------------------------------------------------------------------------
 // One thread moves half a run: 8 consecutive datums of a face row (16 bytes of bf16, 32 of fp32).
 // Datum (r, c) of a tile is at (r / 16 * 2 + c / 16) * 256 + r % 16 * 16 + c % 16.
-template <typename T>
+// WIDE: every row of the row-major side starts on a 16-byte boundary and cols is a multiple of 8, so the 8 datums
+// move as whole 16-byte words.
+template <typename T, bool WIDE>
 __global__ void tilize_kernel(const T *__restrict__ src, T *__restrict__ dst, int batch, int rows, int cols, int tr, int tc) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;          // half-run index in the tiled image
   size_t total = (size_t)batch * tr * tc * 128;
@@ -25,17 +27,23 @@ __global__ void tilize_kernel(const T *__restrict__ src, T *__restrict__ dst, in
   if (rows == 1) r = 0;                                              // a single row fills its tile
   __align__(16) T out[8];
   const T *row = src + ((size_t)b * rows + r) * cols;
+  if (WIDE) {
 #pragma unroll
-  for (int k = 0; k < 8; k++) {
-    int c = cols == 1 ? 0 : c0 + k;                                  // a single column repeats
-    out[k] = (r < rows && c < cols) ? row[c] : T(0);
+    for (int k = 0; k < (int)(sizeof(out) / 16); k++)
+      reinterpret_cast<uint4 *>(out)[k] = r < rows && c0 < cols ? reinterpret_cast<const uint4 *>(row + c0)[k] : make_uint4(0, 0, 0, 0);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      int c = cols == 1 ? 0 : c0 + k;                                // a single column repeats
+      out[k] = (r < rows && c < cols) ? row[c] : T(0);
+    }
   }
   uint4 *o = reinterpret_cast<uint4 *>(dst + i * 8);
 #pragma unroll
   for (int k = 0; k < (int)(sizeof(out) / 16); k++) o[k] = reinterpret_cast<const uint4 *>(out)[k];
 }
 
-template <typename T>
+template <typename T, bool WIDE>
 __global__ void untilize_kernel(const T *__restrict__ src, T *__restrict__ dst, int batch, int rows, int cols, int tr, int tc) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t total = (size_t)batch * tr * tc * 128;
@@ -49,9 +57,16 @@ __global__ void untilize_kernel(const T *__restrict__ src, T *__restrict__ dst, 
 #pragma unroll
   for (int k = 0; k < (int)(sizeof(in) / 16); k++) reinterpret_cast<uint4 *>(in)[k] = reinterpret_cast<const uint4 *>(src + i * 8)[k];
   T *row = dst + ((size_t)b * rows + r) * cols;
+  if (WIDE) {
+    if (c0 < cols) {
 #pragma unroll
-  for (int k = 0; k < 8; k++)
-    if (c0 + k < cols) row[c0 + k] = in[k];
+      for (int k = 0; k < (int)(sizeof(in) / 16); k++) reinterpret_cast<uint4 *>(row + c0)[k] = reinterpret_cast<const uint4 *>(in)[k];
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; k++)
+      if (c0 + k < cols) row[c0 + k] = in[k];
+  }
 }
 
 // fp32 bits -> bf16 bits, round to nearest even; a NaN keeps a quiet payload.
@@ -255,8 +270,16 @@ int bt_tilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, i
   if (int s = use_device(device)) return s;
   int tr = (rows + 31) / 32, tc = (cols + 31) / 32;
   size_t items = (size_t)batch * tr * tc * 128;
-  if (itemsize == 2) tilize_kernel<uint16_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
-  else tilize_kernel<uint32_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+  const bool wide = cols % 8 == 0 && src % 16 == 0 && dst % 16 == 0;
+  const unsigned blocks = blocks_for(items);
+  cudaStream_t st = as_stream(stream);
+  if (itemsize == 2) {
+    if (wide) tilize_kernel<uint16_t, true><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
+    else tilize_kernel<uint16_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
+  } else {
+    if (wide) tilize_kernel<uint32_t, true><<<blocks, kThreads, 0, st>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+    else tilize_kernel<uint32_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+  }
   return launched("tilize_kernel");
 }
 
@@ -267,8 +290,16 @@ int bt_untilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch,
   if (int s = use_device(device)) return s;
   int tr = (rows + 31) / 32, tc = (cols + 31) / 32;
   size_t items = (size_t)batch * tr * tc * 128;
-  if (itemsize == 2) untilize_kernel<uint16_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
-  else untilize_kernel<uint32_t><<<blocks_for(items), kThreads, 0, as_stream(stream)>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+  const bool wide = cols % 8 == 0 && src % 16 == 0 && dst % 16 == 0;
+  const unsigned blocks = blocks_for(items);
+  cudaStream_t st = as_stream(stream);
+  if (itemsize == 2) {
+    if (wide) untilize_kernel<uint16_t, true><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
+    else untilize_kernel<uint16_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
+  } else {
+    if (wide) untilize_kernel<uint32_t, true><<<blocks, kThreads, 0, st>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+    else untilize_kernel<uint32_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
+  }
   return launched("untilize_kernel");
 }
 

@@ -243,7 +243,7 @@ class Tensor:
     if self.dtype != "bf16" or x.dtype not in BFP:
       raise ValueError(f"this backend multiplies bf16 A by a block-float B, not {self.dtype} @ {x.dtype}")
     if dtype not in (None, "bf16", "fp32"): raise ValueError(f"matmul results are bf16 or fp32, not {dtype}")
-    if self.cols % 32 or x.cols % 32: raise ValueError(f"this backend's matmul needs K and N in multiples of 32: {self.shape} @ {x.shape}")
+    if self.cols == 1: raise ValueError(f"this backend's matmul needs more than one column of A: {self.shape} @ {x.shape}")
     return self._node("matmul", (self, x), cols=x.cols, dtype=dtype or "bf16")
 
   def topk(self, k, parts=1, labels=None):
@@ -365,18 +365,20 @@ def _launch_matmul(rt, e, epilogue, out, rows, arg=(0, 0), arg_base=0):
   x, w = e["x"].realize(), _streamed(e["w"])
   w2 = _streamed(e["w2"]) if e.get("w2") is not None else None
   add = e["add"].realize() if e["add"] is not None else None
-  fmt, K, N = FMT_CODE[w.dtype], x.cols, w.cols
+  # both kernels work on whole tiles: the padding of x, of the weights and of the addend is zero, and so is the result's
+  fmt, K, N = FMT_CODE[w.dtype], x.tc * 32, w.tc * 32
+  if epilogue == "argmax" and w.cols % 32: raise ValueError("the fused pick needs N in multiples of 32 (a padding column's zero could win)")
   out_dtype = FMT_CODE[out.dtype] if out is not None else 0
   osize = tile_bytes(out.dtype) if out is not None else 0
   name = f"matmul {w.dtype} {epilogue}"
   if epilogue == "argmax" and rows > 32: raise ValueError("the fused pick takes up to 32 rows")
-  if rows > 32 and add is None and epilogue != "argmax" and K % 64 == 0 and N % (128 if w2 else 256) == 0:
-    # many rows: the tensor-core kernel, which reads x row-major
+  if rows > 32 and epilogue != "argmax":
+    # many rows: the tensor-core kernel, which reads x row-major, whole tiles wide
     flat = rt.dram_alloc(2 * rows * K)
     try:
       rt.launch("bt_untilize", (2, x.addr, flat, 1, rows, K), name="rows")
-      rt.launch("bt_gemm_bfp", (fmt, EPILOGUE[epilogue], rows, K, N, flat, w.addr, w2.addr if w2 else 0, ctypes.c_float(e["alpha"]),
-                                out.addr, out_dtype, rt.work), name=f"prefill {w.dtype} {epilogue}")
+      rt.launch("bt_gemm_bfp", (fmt, EPILOGUE[epilogue], rows, K, w.cols, flat, w.addr, w2.addr if w2 else 0, add.addr if add else 0,
+                                add.rows if add else 0, ctypes.c_float(e["alpha"]), out.addr, out_dtype, rt.work), name=f"prefill {w.dtype} {epilogue}")
     finally: rt.dram_free(flat)
     return
   for i in range(0, rows, 32):   # one launch per tile row of x; each streams W once

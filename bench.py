@@ -169,6 +169,7 @@ def main():
   ap.add_argument("--quick", action="store_true", help="4096x4096 only (profiling captures)")
   ap.add_argument("--only", default="", help="run one case of the sweep, as KxN:fmt:M:pair, e.g. 4096x14336:bfp8:8:0 (profiling captures)")
   ap.add_argument("--prefill-rows", type=int, default=2048, help="rows of the prefill leg; 0 skips it")
+  ap.add_argument("--prefill-only", action="store_true", help="of the legs beside the headline, only the prefill one (profiling captures)")
   args = ap.parse_args()
   rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
   if args.impl == "reference": return run_reference(args, rank)
@@ -338,10 +339,11 @@ def main():
   clock = clocks.stop() if clocks else None
 
   extras = world == 1 and not args.quick and not args.only and not args.no_extras
+  decode_extras = extras and not args.prefill_only
 
   # ---- a decode layer chain: every matmul reads the one before it (what a decode step pays at the boundaries) ----
   chain = None
-  if extras:
+  if decode_extras:
     chain = []
     layers = 32
     for fmt in FORMATS:
@@ -376,7 +378,7 @@ def main():
 
   # ---- one large matmul alone (Llama-3-70B gate shape, 8192 x 28672): the kernel without the boundaries ----
   big = None
-  if extras:
+  if decode_extras:
     big = []
     for fmt in FORMATS:
       src = weight(4096, 14336, fmt, "gate")
@@ -401,7 +403,7 @@ def main():
 
   # ---- the byte kernels either side of the matmul, on a 4096 x 14336 matrix, against the same HBM peak ----
   byte_kernels = None
-  if extras:
+  if decode_extras:
     byte_kernels = []
     k, n = 4096, 14336
     values = k * n

@@ -153,15 +153,18 @@ int bt_gemv_queue(int device, int n, const bt_gemv_op *ops, uint64_t work, size_
  * before it (-1). */
 int bt_gemv_queue_plan(int n, const bt_gemv_op *ops, int *waits);
 /* ---- the matmul: fused_kernel's prefill grid (baretile/kernels.py:205-215, :470-506, grid_parts :18-39) ----
- * out[M, N] = epilogue(alpha * (a[M, K] @ W[K, N])) for many rows, on the tcgen05 tensor cores with fp32
- * accumulators in tensor memory. The weights are expanded from block float to exact bf16 inside the kernel.
- *   a      bf16, ROW-MAJOR [M, K] (bt_untilize of the tile-layout tensor); K a multiple of 64.
- *   w, w2  block-float weights in streaming layout; w2 only for BT_EPI_GLU (out = silu(a @ w) * (a @ w2)).
- *          N a multiple of 256, or of 128 for the pair.
+ * out[M, N] = epilogue(alpha * (a[M, K] @ W[K, N]) + add) for many rows, on the tcgen05 tensor cores with fp32
+ * accumulators in tensor memory, two CTAs to an MMA. The weights are expanded from block float to exact bf16
+ * inside the kernel.
+ *   a      bf16, ROW-MAJOR [M, K] (bt_untilize of the tile-layout tensor, over whole tiles: K a multiple of 32,
+ *          columns past the tensor's own holding zeros).
+ *   w, w2  block-float weights in streaming layout; w2 only for BT_EPI_GLU (out = silu(a @ w + add) * (a @ w2)).
+ *          N is the tensor's own column count, any positive number.
+ *   add    0, or bf16 tiles of an addend of add_rows (M or 1) x N, added before the activation.
  *   out    bf16 or fp32 tiles, rows past M zero.
  *   work   the matmul scratch (bt_gemv_workspace_bytes): only its error word is used. */
-int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t a, uint64_t w, uint64_t w2, float alpha,
-                uint64_t out, int out_dtype, uint64_t work, uint64_t stream);
+int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t a, uint64_t w, uint64_t w2, uint64_t add,
+                int add_rows, float alpha, uint64_t out, int out_dtype, uint64_t work, uint64_t stream);
 
 /* The same matmul for callers that cannot allocate device memory: it has no counterpart in the reference.
  * Some embedders of this library run where cudaMalloc is off limits -- inside another framework's capture or

@@ -30,8 +30,10 @@ def run(rt, x, w, fmt, epilogue="none", w2=None, dtype=None, columns=True, add=N
   got = y.realize()
   rt.wait()
   names, rt.log = [name for *_, name in rt.log], None
-  # one matmul launch per tile row of x, with the epilogue fused; a B not yet by columns is first laid out, once
-  assert sum(n.startswith("matmul") for n in names) == -(-x.shape[0] // 32) and len(names) <= -(-x.shape[0] // 32) + (0 if columns else 2)
+  # one matmul launch with the epilogue fused (up to 32 rows: the decode kernel; more: the tensor-core kernel after
+  # x is laid out by rows); a B not yet by columns is first laid out, once
+  many = x.shape[0] > 32
+  assert sum(n.startswith("prefill" if many else "matmul") for n in names) == 1 and len(names) <= 1 + many + (0 if columns else 2), names
   out = got.numpy()
   if epilogue in ("none", "relu"):   # every element within 2^-8 of sum |x||w| (+ |addend|): the reference's per-element bound
     check_matmul(out, x, wd, ref, TOL_BF16 if dtype != "fp32" else TOL_FP32, addend=add, alpha=alpha if alpha is not None else 1.0)
