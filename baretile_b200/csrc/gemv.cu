@@ -927,7 +927,7 @@ constexpr size_t kStKeys = 256;
 constexpr size_t kStCounters = 512;
 constexpr size_t kStControlBytes = kStCounters + 4 * (size_t)kStaticSubPanels;   // what must be zero when a call starts
 constexpr size_t kStPartials = kStControlBytes;
-constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 0.7 MB
+constexpr size_t kStaticBytes = kStPartials + (size_t)kMaxCtas * kStaticSlotFloats * 4;   // about 2.6 MB
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 

@@ -170,7 +170,7 @@ int bt_gemm_bfp(int device, int fmt, int epilogue, int M, int K, int N, uint64_t
  * Some embedders of this library run where cudaMalloc is off limits -- inside another framework's capture or
  * allocator-owned region, in a process whose memory budget was handed out in full at start-up, or in a plug-in
  * that is only ever given its input and output buffers. For them the scratch that bt_gemv_bfp takes from the
- * caller sits in a fixed array inside the library's device image (about 0.7 MB on every GPU that loads the
+ * caller sits in a fixed array inside the library's device image (about 2.6 MB on every GPU that loads the
  * library, held until the process exits). The call allocates and frees nothing, on the host side either.
  * Limits, rejected with BT_BAD_ARGUMENT: M <= 8 rows of x, N <= 524288 columns. Inputs and outputs are the
  * caller's, exactly as for bt_gemv_bfp. The first call on a device looks the array's address up (one runtime

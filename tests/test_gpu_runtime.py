@@ -116,7 +116,32 @@ def test_wait_times_out_and_the_runtime_stays_usable(rt):
   finally: rt.dram_free(big)
 
 
-def test_bounded_device_wait_reports_instead_of_hanging(rt):
+def test_bounded_wait_for_an_earlier_matmul_reports_instead_of_hanging(rt):
+  # A wait inside the matmul kernel that cannot be met gives up after its limit and sets the error word, which
+  # Runtime.wait turns into RuntimeError; the kernel ends normally and the runtime keeps working. The wait is made
+  # unmeetable on the host: a matmul of a queue takes its x only when every CTA has reported the matmul two places
+  # before it finished, and that count (one int per matmul of a launch, from byte 8 of the workspace: kWsOpsDone in
+  # csrc/gemv.cu) starts far below zero for the first matmul, so the third one's x warp never sees it complete.
+  from helpers import acts, upload, weights
+  from oracle import bfp_oracle as o
+  rng = np.random.default_rng(5)
+  x, w = acts(rng, 4, 4096), weights(rng, 4096, 512)               # 4 sub-panels, each shared by many CTAs
+  tx, tw = upload(rt, x), upload(rt, w).cast("bfp8").columns()
+  def three():
+    with rt.queue(): return [(tx @ tw).realize() for _ in range(3)]
+  good = [y.numpy() for y in three()]
+  rt.wait()
+  rt.upload(rt.work + 8, bytes((ctypes.c_int * 1)(-1000)))
+  ys = three()
+  with pytest.raises(RuntimeError, match="gave up on a bounded wait"): rt.wait()
+  rt.wait()                                                        # the flag was read and cleared, the counts reset
+  again = [y.numpy() for y in three()]
+  assert all(np.array_equal(a, g) for a, g in zip(again, good))
+  assert o.rel_err(good[0], x @ o.dequant(w, "bfp8")) <= 1e-2
+  del ys
+
+
+def test_bounded_wait_for_partial_sums_reports_instead_of_hanging(rt):
   # A wait inside the matmul kernel that cannot be met gives up after its limit and sets the error word, which
   # Runtime.wait turns into RuntimeError; the kernel ends normally and the runtime keeps working. The wait is made
   # unmeetable on the host: the arrival counters of the matrix' sub-panels in the scratch start far below zero, so
