@@ -80,6 +80,9 @@ def gather_argmax(values, indices, group=None):
 # Everything below goes through the C-ABI on the runtime's stream: matmul launches, NCCL collectives (bt_allgather,
 # bt_allreduce_sum) and the small kernels either side of them, with no torch operation on the data path.
 
+BT_PEER_DATA = 4096   # bytes the library keeps at the start of a peer buffer (include/baretile_b200.h)
+
+
 class Comm:
   """The ranks' NCCL communicator behind the C-ABI (bt_comm_init). `exchange(bytes)` hands rank 0's bytes to every
   rank: by default over torch.distributed (any backend), which is only used for this one hand-shake."""
@@ -98,9 +101,22 @@ class Comm:
     handle = ctypes.c_uint64()
     _lib.call("bt_comm_init", rt.device, rank, world, uid, ctypes.byref(handle))
     self.handle = handle.value
+    self.opened = []
+
+  def open_peers(self, size):
+    """A buffer of BT_PEER_DATA + size bytes on every rank, mapped on all of them (bt_peer_open): the ranks' addresses
+    as a ctypes array for the peer entry points. Collective: every rank calls it with the same size."""
+    import ctypes
+    from baretile_b200 import _lib
+    peers = (ctypes.c_uint64 * self.world)()
+    _lib.call("bt_peer_open", self.rt.device, self.handle, self.rank, self.world, size, peers, self.rt.stream)
+    self.opened.append(peers)
+    return peers
 
   def close(self):
     from baretile_b200 import _lib
+    for peers in self.opened: _lib.call("bt_peer_close", self.rt.device, self.handle, self.rank, self.world, peers, self.rt.stream)
+    self.opened = []
     if self.handle: _lib.lib().bt_comm_destroy(self.handle)
     self.handle = 0
 
@@ -114,10 +130,14 @@ class ShardedMLP:
   projection writes fp32 partial sums row-major, one all-reduce adds them over the ranks and one small kernel rounds
   them to bf16 tiles. With gather=True the gate/up result is also all-gathered to [M, N], as a stand-alone
   column-parallel layer would do (the tile buffers of the ranks, one after another, are the full tensor's tile row);
-  the down projection needs only the rank's own slice either way."""
-  def __init__(self, rt, wg, wu, wd, comm):
+  the down projection needs only the rank's own slice either way.
+  With peer=True the all-reduce and the rounding are one kernel over peer memory instead (bt_peer_allreduce_round): the
+  partial sums go into a buffer the other ranks map, alternating between its two halves from step to step."""
+  def __init__(self, rt, wg, wu, wd, comm, peer=False):
     self.rt, self.wg, self.wu, self.wd, self.comm = rt, wg, wu, wd, comm
-    self.partial = rt.dram_alloc(4 * 32 * wd.cols)
+    self.half = 4 * 32 * wd.cols
+    self.peers, self.step = (comm.open_peers(2 * self.half) if peer else None), 0
+    self.partial = None if peer else rt.dram_alloc(self.half)
     self.gathered = None
 
   def forward(self, x, gather=False):
@@ -125,15 +145,21 @@ class ShardedMLP:
     from baretile_b200.tensor import Tensor, FMT_CODE
     rt, m = self.rt, x.rows
     out = Tensor(rt, m, self.wd.cols)
+    self.step += 1
+    offset = (self.step & 1) * self.half
+    partial = self.partial if self.peers is None else self.peers[self.comm.rank] + BT_PEER_DATA + offset
     with rt.queue():
       h = ((x @ self.wg).silu() * (x @ self.wu)).realize()              # [M, N/world] bf16 tiles
       rt.launch("bt_gemv_bfp", (FMT_CODE[self.wd.dtype], 0, m, h.cols, self.wd.cols, h.addr, self.wd.addr, 0, 0, ctypes.c_float(1.0),
-                                self.partial, 16, 0, 0, 0, rt.work, rt.work_bytes), name="matmul down partial")
+                                partial, 16, 0, 0, 0, rt.work, rt.work_bytes), name="matmul down partial")
     if gather:
       if self.gathered is None or self.gathered.cols != h.cols * self.comm.world: self.gathered = Tensor(rt, 32, h.cols * self.comm.world)
       rt.launch("bt_allgather", (self.comm.handle, h.addr, self.gathered.addr, h.tiles * 2048), name="all-gather")
-    rt.launch("bt_allreduce_sum", (self.comm.handle, self.partial, m * self.wd.cols), name="all-reduce")
-    rt.launch("bt_round_tilize", (self.partial, out.addr, m, self.wd.cols), name="round")
+    if self.peers is not None:
+      rt.launch("bt_peer_allreduce_round", (self.comm.rank, self.comm.world, self.peers, offset, self.step, m, self.wd.cols, out.addr), name="peer all-reduce")
+    else:
+      rt.launch("bt_allreduce_sum", (self.comm.handle, self.partial, m * self.wd.cols), name="all-reduce")
+      rt.launch("bt_round_tilize", (self.partial, out.addr, m, self.wd.cols), name="round")
     self.h = h                                                         # its memory is read by the launches above
     return out
 

@@ -468,7 +468,8 @@ def main():
     def shard(rows, cols, seed, fmt): return Tensor.frombytes(rt, rows, cols, np.ascontiguousarray(tiled(rows, cols, seed)).tobytes()).cast(fmt).columns()
     K3, N3, V4 = 8192, 28672, 128256
     a, b = bd.split_tiles(N3, world, rank)
-    mlp = bd.ShardedMLP(rt, shard(K3, b - a, 1, "bfp4"), shard(K3, b - a, 2, "bfp4"), shard(b - a, K3, 3, "bfp4"), comm)
+    slices = (shard(K3, b - a, 1, "bfp4"), shard(K3, b - a, 2, "bfp4"), shard(b - a, K3, 3, "bfp4"))
+    mlp, mlp_peer = bd.ShardedMLP(rt, *slices, comm), bd.ShardedMLP(rt, *slices, comm, peer=True)
     va, vb = bd.split_tiles(V4, world, rank)
     head = bd.ShardedHead(rt, shard(K3, vb - va, 4, "bfp8"), va, comm)
     mlp_bytes, head_bytes = 3 * (K3 // 32) * (N3 // 32) * TILE["bfp4"], (K3 // 32) * (V4 // 32) * TILE["bfp8"]
@@ -481,13 +482,16 @@ def main():
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
       for gather in (True, False):
         us = median_us(lambda: mlp.forward(xs, gather=gather))
-        sharded["mlp"].append({"M": m, "all_gather": gather, "us": us, "GBps_all_ranks": round(mlp_bytes / us / 1e3, 1)})
+        sharded["mlp"].append({"M": m, "all_gather": gather, "exchange": "nccl all-reduce + rounding kernel", "us": us, "GBps_all_ranks": round(mlp_bytes / us / 1e3, 1)})
+      us = median_us(lambda: mlp_peer.forward(xs))
+      sharded["mlp"].append({"M": m, "all_gather": False, "exchange": "one kernel over peer memory", "us": us, "GBps_all_ranks": round(mlp_bytes / us / 1e3, 1)})
     for m in (1, 4, 8):
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
       us = median_us(lambda: head.pick(xs))
       sharded["head"].append({"M": m, "us": us, "GBps_all_ranks": round(head_bytes / us / 1e3, 1)})
-    sharded["note"] = ("configs[3]: gate/up [8192,28672] bfp4 split over N, down [28672,8192] split over K: one queue launch, an all-reduce of "
-                       "fp32 partial sums and a rounding kernel, with or without the all-gather of the gate/up result; configs[4]: LM head "
+    sharded["note"] = ("configs[3]: gate/up [8192,28672] bfp4 split over N, down [28672,8192] split over K: one queue launch, then either an "
+                       "NCCL all-reduce of fp32 partial sums and a rounding kernel (with or without the all-gather of the gate/up result) or one "
+                       "kernel that adds the ranks' partial rows from peer memory, rounds and tiles; configs[4]: LM head "
                        "[8192,128256] bfp8 split over the vocabulary: fused pick, all-gather of 256 bytes per rank, combining kernel")
     rt.wait()
     comm.close()

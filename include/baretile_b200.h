@@ -208,6 +208,27 @@ int bt_comm_destroy(uint64_t comm);
 int bt_allgather(int device, uint64_t comm, uint64_t src, uint64_t dst, size_t bytes, uint64_t stream);
 int bt_allreduce_sum(int device, uint64_t comm, uint64_t buf_f32, size_t count, uint64_t stream);
 int bt_round_tilize(int device, uint64_t src_f32_rows, uint64_t dst_bf16_tiles, int rows, int cols, uint64_t stream);
+
+/* ---- the down projection's exchange as one kernel over peer memory (no counterpart in the reference, like the
+ * collectives above) ----
+ * bt_peer_open gives every rank a buffer of BT_PEER_DATA + bytes that the other ranks of the box map through CUDA IPC
+ * (the handles go round the communicator); peers[r] receives rank r's buffer as an address on this device,
+ * peers[rank] the rank's own. Collective: every rank calls it, with the same bytes. The first BT_PEER_DATA bytes
+ * are the library's (flags, an error word); the caller's rows live behind them.
+ * bt_peer_allreduce_round(step): every rank has written rows x cols fp32, row-major, at BT_PEER_DATA + offset of its
+ * own buffer (a matmul with out_dtype BT_FP32_ROWS does); the kernel announces them to the peers, waits (about a
+ * second at most) for theirs, adds all ranks' rows in rank order straight from their memories, rounds half up and
+ * writes bf16 tiles of one tile row to dst. step grows by one per call, on every rank alike, starting at 1; the
+ * caller alternates offset between two halves of the buffer from step to step (a rank is never more than one
+ * step ahead of a peer, so the half it overwrites has been read by all). bt_peer_check reads (and clears) the word a
+ * wait that gave up sets. bt_peer_close is collective too: it waits until every rank has got past its kernels that read
+ * the others' rows, then unmaps and frees. */
+#define BT_PEER_DATA 4096
+int bt_peer_open(int device, uint64_t comm, int rank, int world, size_t bytes, uint64_t *peers, uint64_t stream);
+int bt_peer_close(int device, uint64_t comm, int rank, int world, const uint64_t *peers, uint64_t stream);
+int bt_peer_allreduce_round(int device, int rank, int world, const uint64_t *peers, size_t offset, int step, int rows, int cols,
+                            uint64_t dst_bf16_tiles, uint64_t stream);
+int bt_peer_check(int device, int rank, const uint64_t *peers, uint64_t stream, int *error);
 int bt_argmax_combine(int device, uint64_t blocks, int world, int rows, uint64_t out_val, uint64_t out_idx, uint64_t stream);
 /* Number of GPU kernels this library has launched on behalf of the calling process. */
 int bt_launch_count(uint64_t *count);

@@ -1,6 +1,6 @@
 """Run under torchrun with one rank per GPU: the sharded MLP and the vocabulary-split greedy pick on real GPUs,
 checked on every rank against the oracle's unsharded fp32 NumPy result. Prints one 'ok' line per rank."""
-import os, sys
+import ctypes, os, sys
 import numpy as np
 import torch.distributed as dist
 
@@ -12,7 +12,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 def main():
   from oracle import bfp_oracle as o
   from helpers import acts, upload, weights
-  from baretile_b200 import dist as bd, pci
+  from baretile_b200 import _lib, dist as bd, pci
   from baretile_b200.chip import Chip
   from baretile_b200.runtime import Runtime
   rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -26,8 +26,8 @@ def main():
     wg, wu, wd = weights(rng, k, n), weights(rng, k, n), weights(rng, n, k)
     a, b = bd.split_tiles(n, world, rank)
     tx = upload(rt, x)
-    mlp = bd.ShardedMLP(rt, upload(rt, wg[:, a:b]).cast("bfp4").columns(), upload(rt, wu[:, a:b]).cast("bfp4").columns(),
-                        upload(rt, wd[a:b]).cast("bfp4").columns(), comm)
+    mine = (upload(rt, wg[:, a:b]).cast("bfp4").columns(), upload(rt, wu[:, a:b]).cast("bfp4").columns(), upload(rt, wd[a:b]).cast("bfp4").columns())
+    mlp = bd.ShardedMLP(rt, *mine, comm)
     h = o.bf16_floats(o.bf16_half_up(o.matmul(x, o.dequant(wg, "bfp4"), "glu", o.dequant(wu, "bfp4"))))
     want = o.matmul(h, o.dequant(wd, "bfp4"))
     for gather in (True, False):
@@ -37,6 +37,19 @@ def main():
       if gather:                                                    # the gathered activations are the unsharded ones
         full = mlp.gathered.numpy()[:m]
         assert o.rel_err(full, h) <= 1e-2, (rank, m, o.rel_err(full, h))
+    # the same layer with the exchange as one kernel over peer memory: several steps in a row (the rows alternate
+    # between the two halves of the peer buffer), the same bits on every rank, and no wait that gave up
+    peer = bd.ShardedMLP(rt, *mine, comm, peer=True)
+    for step in range(5):
+      got = peer.forward(upload(rt, x * (step + 1))).numpy()
+      err = o.rel_err(got, o.matmul(o.bf16_floats(o.bf16_half_up(o.matmul(x * (step + 1), o.dequant(wg, "bfp4"), "glu", o.dequant(wu, "bfp4")))), o.dequant(wd, "bfp4")))
+      assert err <= 1e-2, (rank, m, step, err)
+      everyone = [None] * world
+      dist.all_gather_object(everyone, got.tobytes())
+      assert all(b == everyone[0] for b in everyone), (rank, m, step)
+    gave_up = ctypes.c_int(-1)
+    _lib.call("bt_peer_check", rt.device, rank, peer.peers, rt.stream, ctypes.byref(gave_up))
+    assert gave_up.value == 0
     # LM head: vocabulary split, index-exact against the unsharded fp32 logits of the same kernels' arithmetic
     wv = weights(rng, k, vocab)
     wv[:, 5] = wv[:, vocab - 7]                                     # equal columns on the first and the last rank: a tie
