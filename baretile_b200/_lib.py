@@ -46,6 +46,8 @@ SIGNATURES = {
   "bt_graph_destroy": [i32, u64],
   "bt_tilize": [i32, i32, u64, u64, i32, i32, i32, u64],
   "bt_untilize": [i32, i32, u64, u64, i32, i32, i32, u64],
+  "bt_tilize_many": [i32, i32, i32, ctypes.POINTER(u64), ctypes.POINTER(u64), ctypes.POINTER(i32), ctypes.POINTER(i32), u64],
+  "bt_untilize_many": [i32, i32, i32, ctypes.POINTER(u64), ctypes.POINTER(u64), ctypes.POINTER(i32), ctypes.POINTER(i32), u64],
   "bt_round_bf16": [i32, u64, u64, size_t, u64],
   "bt_pack_bfp": [i32, i32, u64, u64, size_t, u64],
   "bt_unpack_bfp": [i32, i32, u64, u64, size_t, u64],

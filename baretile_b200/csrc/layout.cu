@@ -69,6 +69,50 @@ __global__ void untilize_kernel(const T *__restrict__ src, T *__restrict__ dst, 
   }
 }
 
+// Many small matrices in one launch (a decode step's inputs on their way in, its results on their way out): the table
+// travels by value with the launch, item k owns the half runs [first[k], first[k + 1]), and each thread does what a
+// thread of tilize_kernel / untilize_kernel does for one matrix (batch 1). One launch instead of one per matrix: for
+// matrices of a few tiles the launch is the cost.
+constexpr int kManyMax = 64;
+struct ManyArgs {
+  const void *src[kManyMax];
+  void *dst[kManyMax];
+  int rows[kManyMax], cols[kManyMax], first[kManyMax + 1];
+  int n;
+};
+template <typename T, bool TILIZE>
+__global__ void many_kernel(const ManyArgs a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.first[a.n]) return;
+  int k = 0;
+  while (i >= a.first[k + 1]) k++;
+  const int rows = a.rows[k], cols = a.cols[k], tc = (cols + 31) / 32, h = i - a.first[k];
+  const int tile = h / 128, in = h % 128, face = in / 32, r16 = in % 32 / 2, c8 = in % 2 * 8;
+  int r = tile / tc * 32 + face / 2 * 16 + r16;
+  const int c0 = tile % tc * 32 + face % 2 * 16 + c8;
+  __align__(16) T v[8];
+  if (TILIZE) {
+    if (rows == 1) r = 0;                                              // a single row fills its tile
+    const T *row = static_cast<const T *>(a.src[k]) + (size_t)r * cols;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int c = cols == 1 ? 0 : c0 + j;                            // a single column repeats
+      v[j] = (r < rows && c < cols) ? row[c] : T(0);
+    }
+    uint4 *o = reinterpret_cast<uint4 *>(static_cast<T *>(a.dst[k]) + (size_t)h * 8);
+#pragma unroll
+    for (int j = 0; j < (int)(sizeof(v) / 16); j++) o[j] = reinterpret_cast<const uint4 *>(v)[j];
+  } else {
+    if (r >= rows) return;
+#pragma unroll
+    for (int j = 0; j < (int)(sizeof(v) / 16); j++) reinterpret_cast<uint4 *>(v)[j] = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.src[k]) + (size_t)h * 8)[j];
+    T *row = static_cast<T *>(a.dst[k]) + (size_t)r * cols;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (c0 + j < cols) row[c0 + j] = v[j];
+  }
+}
+
 // fp32 bits -> bf16 bits, round to nearest even; a NaN keeps a quiet payload.
 __global__ void round_bf16_kernel(const uint32_t *__restrict__ src, uint16_t *__restrict__ dst, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -301,6 +345,44 @@ int bt_untilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch,
     else untilize_kernel<uint32_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc);
   }
   return launched("untilize_kernel");
+}
+
+static int many(const char *what, bool tilize, int device, int itemsize, int n, const uint64_t *src, const uint64_t *dst, const int *rows, const int *cols,
+                uint64_t stream) {
+  BT_REQUIRE(itemsize == 2 || itemsize == 4, "%s: itemsize must be 2 or 4, not %d", what, itemsize);
+  BT_REQUIRE(n > 0 && src && dst && rows && cols, "%s: null table or no matrices", what);
+  if (int s = use_device(device)) return s;
+  for (int at = 0; at < n; at += kManyMax) {
+    ManyArgs a{};
+    a.n = min(kManyMax, n - at);
+    for (int k = 0; k < a.n; k++) {
+      if (int s = check_shape(what, 1, rows[at + k], cols[at + k])) return s;
+      BT_REQUIRE(src[at + k] && dst[at + k] && (tilize ? dst : src)[at + k] % 16 == 0, "%s: matrix %d: null address or tiles not 16-byte aligned", what, at + k);
+      a.src[k] = as_ptr<void>(src[at + k]), a.dst[k] = as_ptr<void>(dst[at + k]), a.rows[k] = rows[at + k], a.cols[k] = cols[at + k];
+      const long long halves = (long long)((rows[at + k] + 31) / 32) * ((cols[at + k] + 31) / 32) * 128;
+      BT_REQUIRE(a.first[k] + halves < (1ll << 31), "%s: too much for one launch: put large matrices through the single-matrix call", what);
+      a.first[k + 1] = a.first[k] + (int)halves;
+    }
+    const unsigned blocks = blocks_for((size_t)a.first[a.n]);
+    cudaStream_t st = as_stream(stream);
+    if (itemsize == 2) {
+      if (tilize) many_kernel<uint16_t, true><<<blocks, kThreads, 0, st>>>(a);
+      else many_kernel<uint16_t, false><<<blocks, kThreads, 0, st>>>(a);
+    } else {
+      if (tilize) many_kernel<uint32_t, true><<<blocks, kThreads, 0, st>>>(a);
+      else many_kernel<uint32_t, false><<<blocks, kThreads, 0, st>>>(a);
+    }
+    if (int s = launched("many_kernel")) return s;
+  }
+  return BT_OK;
+}
+
+int bt_tilize_many(int device, int itemsize, int n, const uint64_t *src, const uint64_t *dst, const int *rows, const int *cols, uint64_t stream) {
+  return many("bt_tilize_many", true, device, itemsize, n, src, dst, rows, cols, stream);
+}
+
+int bt_untilize_many(int device, int itemsize, int n, const uint64_t *src, const uint64_t *dst, const int *rows, const int *cols, uint64_t stream) {
+  return many("bt_untilize_many", false, device, itemsize, n, src, dst, rows, cols, stream);
 }
 
 int bt_round_bf16(int device, uint64_t src_f32, uint64_t dst_bf16, size_t count, uint64_t stream) {

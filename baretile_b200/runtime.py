@@ -323,6 +323,15 @@ class Runtime:
     self.flush()
     _lib.call("bt_d2h", self.device, ctypes.addressof(buf), addr, len(buf) if n is None else n, self.stream)
 
+  def layout_many(self, tilize, items, itemsize=2):
+    """Queue ONE launch that brings many small matrices from row-major order into tile layout (tilize) or back:
+    items = [(src address, dst address, rows, cols), ...]. For a decode step's inputs and results, where a launch per
+    matrix costs more than the work (bt_tilize_many / bt_untilize_many)."""
+    n = len(items)
+    src, dst = (ctypes.c_uint64 * n)(*(int(i[0]) for i in items)), (ctypes.c_uint64 * n)(*(int(i[1]) for i in items))
+    rows, cols = (ctypes.c_int * n)(*(i[2] for i in items)), (ctypes.c_int * n)(*(i[3] for i in items))
+    self.launch("bt_tilize_many" if tilize else "bt_untilize_many", (itemsize, n, src, dst, rows, cols), name="upload" if tilize else "readback")
+
   def upload(self, addr, data):
     """Copy host bytes to device memory at addr, in order with the queued launches."""
     self.check()

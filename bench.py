@@ -228,7 +228,8 @@ def main():
   kernels_before = kernels_launched()
   with rt.record() as step:
     for c in work: outs.append(expression(c).realize())
-  kernels_in_recording = kernels_launched() - kernels_before
+    rt.flush()                                 # the queue launch leaves here, into the recording
+    kernels_in_recording = kernels_launched() - kernels_before   # (counted before the block's end runs the recording once)
   recorded, rt.log = rt.log, None            # (entry point, arguments) of each launch, to time them one by one below
   assert len(recorded) == len(work) == step.count      # the recording sends them as one queue launch
   def barrier():
@@ -313,14 +314,14 @@ def main():
   host_in, host_out = rt.host_alloc(in_bytes), rt.host_alloc(out_bytes)
   for at, c in zip(in_at, work): ctypes.memmove(ctypes.addressof(host_in) + at, c["xh"].ctypes.data, c["xh"].nbytes)
   stage_in, stage_out = rt.dram_alloc(in_bytes), rt.dram_alloc(out_bytes)
-  # The step is recorded once (the copies from and to the page-locked buffers, the layout kernels and the queue
-  # launch) and replayed: what the reference's tensor.jit does for a decode step. The caller writes its inputs into
+  # The step is recorded once (the copies from and to the page-locked buffers, one layout kernel each way and the
+  # queue launch: five nodes) and replayed: what the reference's tensor.jit does for a decode step. The caller writes its inputs into
   # the page-locked buffer before a replay and reads the results from the other after wait().
   with rt.record() as e2e_recording:
     rt.upload_async(stage_in, host_in)
-    for c, at in zip(work, in_at): rt.launch("bt_tilize", (2, stage_in + at, c["x"].addr, 1, c["m"], c["k"]), name="upload")
+    rt.layout_many(True, [(stage_in + at, c["x"].addr, c["m"], c["k"]) for c, at in zip(work, in_at)])       # one launch for all x
     ys = [expression(c).realize() for c in work]
-    for c, y, at in zip(work, ys, out_at): rt.launch("bt_untilize", (2, y.addr, stage_out + at, 1, c["m"], c["n"]), name="readback")
+    rt.layout_many(False, [(y.addr, stage_out + at, c["m"], c["n"]) for c, y, at in zip(work, ys, out_at)])  # and one for all results
     rt.download_async(host_out, stage_out)
   def e2e_step():
     e2e_recording.replay()

@@ -77,6 +77,10 @@ int bt_graph_destroy(int device, uint64_t graph);
  * size 1 repeats across its tile. itemsize is 2 or 4. */
 int bt_tilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, int rows, int cols, uint64_t stream);
 int bt_untilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, int rows, int cols, uint64_t stream);
+/* The same for n small matrices (batch 1 each) in one launch: a decode step's inputs and results, where a launch
+ * per matrix would cost more than the work. src, dst, rows, cols are host arrays of n entries. */
+int bt_tilize_many(int device, int itemsize, int n, const uint64_t *src, const uint64_t *dst, const int *rows, const int *cols, uint64_t stream);
+int bt_untilize_many(int device, int itemsize, int n, const uint64_t *src, const uint64_t *dst, const int *rows, const int *cols, uint64_t stream);
 /* fp32 -> bf16, round to nearest even, NaN kept quiet: tensix.round_bf16 (baretile/tensix.py:240-242). */
 int bt_round_bf16(int device, uint64_t src_f32, uint64_t dst_bf16, size_t count, uint64_t stream);
 

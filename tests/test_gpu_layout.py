@@ -115,3 +115,25 @@ def test_bad_arguments_raise(rt):
   with pytest.raises(ValueError): _lib.call("bt_tilize", rt.device, 3, 256, 256, 1, 1, 1, rt.stream)
   with pytest.raises(ValueError): _lib.call("bt_gemv_bfp", rt.device, 8, 0, 33, 64, 64, 256, 256, 0, 0, 1.0, 256, 0, 0, 0, 0, rt.work, rt.work_bytes, rt.stream)
   rt.wait()                                    # the runtime is still usable
+
+
+def test_many_small_matrices_in_one_launch(rt):
+  # bt_tilize_many / bt_untilize_many give, per matrix, exactly what the single-matrix calls give; more than 64
+  # matrices take several launches; ragged shapes, single rows and single columns included
+  from baretile_b200.tensor import Tensor
+  rng = np.random.default_rng(12)
+  shapes = [(1, 4096), (8, 96), (32, 32), (5, 70), (33, 31), (1, 1), (70, 1), (17, 1000)] * 9          # 72 matrices
+  host = [o.bf16_bits(rng.normal(0, 1, s).astype(np.float32)) for s in shapes]
+  flat = [rt.dram_alloc(h.nbytes) for h in host]
+  for a, h in zip(flat, host): rt.upload(a, h.tobytes())
+  ts = [Tensor(rt, r, c) for r, c in shapes]
+  for t in ts: rt.launch("bt_memset", (t.addr, 0xFF, t.tiles * 2048), name="junk")
+  rt.layout_many(True, [(a, t.addr, t.rows, t.cols) for a, t in zip(flat, ts)])
+  for t, h in zip(ts, host):
+    assert np.array_equal(raw_tiles(rt, t).view(np.uint16), o.tilize(h[None])), t.shape
+  back = [rt.dram_alloc(h.nbytes) for h in host]
+  rt.layout_many(False, [(t.addr, b, t.rows, t.cols) for t, b in zip(ts, back)])
+  rt.wait()
+  for b, h in zip(back, host): assert rt.download(b, h.nbytes) == h.tobytes()
+  for a in flat + back: rt.dram_free(a)
+  with pytest.raises(ValueError, match="no matrices"): rt.layout_many(True, [])
