@@ -152,3 +152,26 @@ def test_queue_collects_matmuls_and_flushes_in_order(monkeypatch):
       matmul(0x10, 0x20)
       raise KeyError("the block fails")
   assert calls == [] and rt.pending is None                          # a failed block sends nothing
+
+
+def test_newer_entry_points_refuse_bad_arguments_before_any_device_work(built):
+  """Argument checks come first in every entry point: they raise ValueError on a box without a GPU too."""
+  import ctypes
+  from baretile_b200 import _lib
+  f = ctypes.c_float(1.0)
+  # prefill matmul: K in whole tiles, w2 only with the gate/up epilogue, an addend of 1 or M rows
+  with pytest.raises(ValueError, match="multiple of 32"): _lib.call("bt_gemm_bfp", 0, 8, 0, 64, 40, 64, 256, 256, 0, 0, 0, f, 256, 0, 256, 0)
+  with pytest.raises(ValueError, match="w2 goes with"): _lib.call("bt_gemm_bfp", 0, 8, 0, 64, 64, 64, 256, 256, 256, 0, 0, f, 256, 0, 256, 0)
+  with pytest.raises(ValueError, match="1 or M rows"): _lib.call("bt_gemm_bfp", 0, 8, 0, 64, 64, 64, 256, 256, 0, 256, 7, f, 256, 0, 256, 0)
+  # put: formats, distinct aligned tensors
+  with pytest.raises(ValueError, match="unknown format"): _lib.call("bt_put", 0, 3, 256, 512, 768, 1, 1, 32, 32, 0)
+  with pytest.raises(ValueError, match="apart from dst"): _lib.call("bt_put", 0, 8, 256, 256, 768, 1, 1, 32, 32, 0)
+  # many small matrices: a table is needed
+  with pytest.raises(ValueError, match="no matrices"): _lib.call("bt_tilize_many", 0, 2, 0, None, None, None, None, 0)
+  with pytest.raises(ValueError, match="itemsize"): _lib.call("bt_untilize_many", 0, 3, 1, None, None, None, None, 0)
+  # the exchange over peer memory: ranks of one box, one tile row of whole tiles, steps from 1
+  peers = (ctypes.c_uint64 * 2)(256, 512)
+  with pytest.raises(ValueError, match="rank"): _lib.call("bt_peer_allreduce_round", 0, 2, 2, peers, 0, 1, 4, 64, 256, 0)
+  with pytest.raises(ValueError, match="step"): _lib.call("bt_peer_allreduce_round", 0, 0, 2, peers, 0, 0, 4, 64, 256, 0)
+  with pytest.raises(ValueError, match="rows at offset"): _lib.call("bt_peer_allreduce_round", 0, 0, 2, peers, 0, 1, 33, 64, 256, 0)
+  with pytest.raises(ValueError, match="up to 8 ranks"): _lib.call("bt_peer_open", 0, 1, 0, 9, 1024, peers, 0)
