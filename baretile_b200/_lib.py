@@ -70,6 +70,7 @@ SIGNATURES = {
   "bt_peer_open": [i32, u64, i32, i32, size_t, ctypes.POINTER(u64), u64],
   "bt_peer_close": [i32, u64, i32, i32, ctypes.POINTER(u64), u64],
   "bt_peer_allreduce_round": [i32, i32, i32, ctypes.POINTER(u64), size_t, i32, i32, i32, u64, u64],
+  "bt_peer_argmax_combine": [i32, i32, i32, ctypes.POINTER(u64), size_t, i32, i32, u64, u64, u64, u64],
   "bt_peer_check": [i32, i32, ctypes.POINTER(u64), u64, ctypes.POINTER(i32)],
   "bt_launch_count": [ctypes.POINTER(u64)],
 }

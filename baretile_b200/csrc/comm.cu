@@ -166,6 +166,55 @@ __global__ void __launch_bounds__(256) peer_allreduce_round_kernel(const PeerArg
   }
 }
 
+// The vocabulary-split pick the same way: this rank's block (32 fp32 values then 32 int32 indices, as the matmul's
+// fused pick leaves them) is stored into slot `rank` of every rank's buffer, this rank's included, then the step is
+// announced; when every rank's step is here, the blocks in the local buffer are combined with the reference's tie
+// rule. One CTA. The slots alternate between two halves of the buffer from step to step, like the rows above.
+struct PeerPickArgs {
+  uint8_t *peer[kPeerMax];
+  size_t data;
+  const uint32_t *mine;
+  float *out_val;
+  int *out_idx;
+  int rank, world, step, rows;
+};
+__global__ void __launch_bounds__(kPeerMax * 64) peer_argmax_combine_kernel(const PeerPickArgs a) {
+  __shared__ int gave_up;
+  const int to = threadIdx.x / 64, word = threadIdx.x % 64;
+  if (threadIdx.x == 0) gave_up = 0;
+  if (to < a.world) {
+    volatile uint32_t *slot = reinterpret_cast<volatile uint32_t *>(a.peer[to] + a.data) + a.rank * 64;
+    slot[word] = a.mine[word];
+    __threadfence_system();                                          // the block before the flag, as the peer sees them
+  }
+  __syncthreads();
+  if (threadIdx.x < a.world && (int)threadIdx.x != a.rank) st_release_sys(reinterpret_cast<int *>(a.peer[threadIdx.x] + kPeerFlags) + a.rank, a.step);
+  if (threadIdx.x < a.world && (int)threadIdx.x != a.rank) {
+    const int *flag = reinterpret_cast<const int *>(a.peer[a.rank] + kPeerFlags) + threadIdx.x;
+    uint32_t spins = 0;
+    while (ld_acquire_sys(flag) - a.step < 0) {
+      if (++spins > kPeerSpins) { gave_up = 1; break; }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (gave_up) {
+    if (threadIdx.x == 0) atomicExch(reinterpret_cast<int *>(a.peer[a.rank] + kPeerError), 1);
+    return;
+  }
+  const int m = threadIdx.x;
+  if (m >= a.rows) return;
+  const volatile float *blocks = reinterpret_cast<const volatile float *>(a.peer[a.rank] + a.data);
+  float bv = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  for (int r = 0; r < a.world; r++) {
+    const float v = blocks[r * 64 + m];
+    const int i = reinterpret_cast<const volatile int *>(blocks)[r * 64 + 32 + m];
+    if (beats(v, i, bv, bi)) bv = v, bi = i;
+  }
+  a.out_val[m] = bv, a.out_idx[m] = bi;
+}
+
 }  // namespace
 
 extern "C" {
@@ -291,6 +340,22 @@ int bt_peer_allreduce_round(int device, int rank, int world, const uint64_t *pee
   const int quads = cols / 32 * 256, blocks = min(148, (quads + 255) / 256);
   peer_allreduce_round_kernel<<<blocks, 256, 0, as_stream(stream)>>>(a);
   return launched("peer_allreduce_round_kernel");
+}
+
+int bt_peer_argmax_combine(int device, int rank, int world, const uint64_t *peers, size_t offset, int step, int rows, uint64_t block, uint64_t out_val,
+                           uint64_t out_idx, uint64_t stream) {
+  BT_REQUIRE(peers && block && out_val && out_idx && world >= 1 && world <= kPeerMax && rank >= 0 && rank < world, "bt_peer_argmax_combine: rank %d of %d", rank, world);
+  BT_REQUIRE(rows >= 1 && rows <= 32 && offset % 16 == 0 && step > 0 && block % 4 == 0, "bt_peer_argmax_combine: %d rows at offset %zu, step %d", rows, offset, step);
+  if (int s = use_device(device)) return s;
+  PeerPickArgs a{};
+  for (int r = 0; r < world; r++) {
+    BT_REQUIRE(peers[r], "bt_peer_argmax_combine: rank %d's buffer is not mapped", r);
+    a.peer[r] = as_ptr<uint8_t>(peers[r]);
+  }
+  a.data = kPeerData + offset, a.mine = as_ptr<uint32_t>(block), a.out_val = as_ptr<float>(out_val), a.out_idx = as_ptr<int>(out_idx);
+  a.rank = rank, a.world = world, a.step = step, a.rows = rows;
+  peer_argmax_combine_kernel<<<1, kPeerMax * 64, 0, as_stream(stream)>>>(a);
+  return launched("peer_argmax_combine_kernel");
 }
 
 int bt_peer_check(int device, int rank, const uint64_t *peers, uint64_t stream, int *error) {

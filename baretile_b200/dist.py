@@ -169,9 +169,11 @@ class ShardedHead:
   `base` the global index of its first column. pick(x) queues the matmul with its fused pick, the all-gather of the
   ranks' 256-byte candidate blocks and the combining kernel, and returns the device address of the result: M fp32
   values followed, 128 bytes in, by M int32 indices, identical on every rank. read() brings them to the host."""
-  def __init__(self, rt, w, base, comm):
+  def __init__(self, rt, w, base, comm, peer=False):
     self.rt, self.w, self.base, self.comm = rt, w, base, comm
     self.mine, self.all, self.out = rt.dram_alloc(256), rt.dram_alloc(256 * comm.world), rt.dram_alloc(256)
+    self.half = 256 * comm.world
+    self.peers, self.step = (comm.open_peers(2 * self.half) if peer else None), 0     # peer=True: the exchange over peer memory
 
   def pick(self, x):
     import ctypes
@@ -179,6 +181,11 @@ class ShardedHead:
     rt, m = self.rt, x.rows
     rt.launch("bt_gemv_bfp", (FMT_CODE[self.w.dtype], 4, m, x.cols, self.w.cols, x.addr, self.w.addr, 0, 0, ctypes.c_float(1.0), 0, 0,
                               self.mine, self.mine + 128, self.base, rt.work, rt.work_bytes), name="matmul pick")
+    if self.peers is not None:
+      self.step += 1
+      rt.launch("bt_peer_argmax_combine", (self.comm.rank, self.comm.world, self.peers, (self.step & 1) * self.half, self.step, m, self.mine,
+                                           self.out, self.out + 128), name="peer combine")
+      return self.out
     rt.launch("bt_allgather", (self.comm.handle, self.mine, self.all, 256), name="all-gather")
     rt.launch("bt_argmax_combine", (self.all, self.comm.world, m, self.out, self.out + 128), name="combine")
     return self.out

@@ -232,6 +232,12 @@ int bt_peer_open(int device, uint64_t comm, int rank, int world, size_t bytes, u
 int bt_peer_close(int device, uint64_t comm, int rank, int world, const uint64_t *peers, uint64_t stream);
 int bt_peer_allreduce_round(int device, int rank, int world, const uint64_t *peers, size_t offset, int step, int rows, int cols,
                             uint64_t dst_bf16_tiles, uint64_t stream);
+/* The vocabulary-split pick over peer memory: `block` is this rank's 256 bytes as the matmul's fused pick leaves
+ * them (32 fp32 values, then 32 int32 indices); they go into slot `rank` (256 bytes each, from BT_PEER_DATA + offset)
+ * of every rank's buffer, and when every rank's block of this step is here they are combined as bt_argmax_combine
+ * combines them. The buffer holds 2 x world x 256 bytes: offset alternates between its halves from step to step. */
+int bt_peer_argmax_combine(int device, int rank, int world, const uint64_t *peers, size_t offset, int step, int rows, uint64_t block,
+                           uint64_t out_val, uint64_t out_idx, uint64_t stream);
 int bt_peer_check(int device, int rank, const uint64_t *peers, uint64_t stream, int *error);
 int bt_argmax_combine(int device, uint64_t blocks, int world, int rows, uint64_t out_val, uint64_t out_idx, uint64_t stream);
 /* Number of GPU kernels this library has launched on behalf of the calling process. */

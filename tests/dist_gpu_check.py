@@ -63,6 +63,14 @@ def main():
     near = (gap <= 2.0 ** -8 * (np.abs(x) @ np.abs(o.dequant(wv, "bfp8"))).max(-1)) & (gap > 0)
     assert np.array_equal(got_ids[~near], ref[~near]), (rank, m, got_ids, ref)
     assert o.rel_err(vals, logits.max(-1)) < 1e-3
+    # the same pick with the exchange over peer memory: the same answer, bit for bit, step after step
+    head_p = bd.ShardedHead(rt, head.w, va, comm, peer=True)
+    for step in range(3):
+      head_p.pick(tx)
+      vals_p, ids_p = head_p.read(m)
+      assert np.array_equal(ids_p, got_ids) and np.array_equal(vals_p, vals), (rank, m, step, ids_p, got_ids)
+    _lib.call("bt_peer_check", rt.device, rank, head_p.peers, rt.stream, ctypes.byref(gave_up))
+    assert gave_up.value == 0
   rt.wait()
   every = [None] * world
   dist.all_gather_object(every, "ok")

@@ -175,3 +175,4 @@ def test_newer_entry_points_refuse_bad_arguments_before_any_device_work(built):
   with pytest.raises(ValueError, match="step"): _lib.call("bt_peer_allreduce_round", 0, 0, 2, peers, 0, 0, 4, 64, 256, 0)
   with pytest.raises(ValueError, match="rows at offset"): _lib.call("bt_peer_allreduce_round", 0, 0, 2, peers, 0, 1, 33, 64, 256, 0)
   with pytest.raises(ValueError, match="up to 8 ranks"): _lib.call("bt_peer_open", 0, 1, 0, 9, 1024, peers, 0)
+  with pytest.raises(ValueError, match="rows at offset"): _lib.call("bt_peer_argmax_combine", 0, 0, 2, peers, 0, 1, 40, 256, 256, 512, 0)
