@@ -51,7 +51,7 @@ SIGNATURES = {
   "bt_round_bf16": [i32, u64, u64, size_t, u64],
   "bt_pack_bfp": [i32, i32, u64, u64, size_t, u64],
   "bt_unpack_bfp": [i32, i32, u64, u64, size_t, u64],
-  "bt_put": [i32, i32, u64, u64, u64, i32, i32, i32, i32, u64],
+  "bt_put": [i32, i32, u64, u64, u64, i32, i32, i32, i32, u64, u64],
   "bt_relayout": [i32, i32, i32, i32, i32, u64, u64, u64],
   "bt_gemv_workspace_bytes": [i32, ctypes.POINTER(size_t)],
   "bt_gemv_bfp": [i32, i32, i32, i32, i32, i32, u64, u64, u64, u64, f32, u64, i32, u64, u64, i32, u64, size_t, u64],

@@ -180,18 +180,33 @@ __global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__
 // exponent, its values), so nothing is read back or merged. A destination of one logical row keeps that row in all
 // 32 rows of its tile, so there every place inside the tile writes all 32 (and the last such row of x wins).
 // ids is an int32 row in tile layout: place i is datum (0, i % 32) of tile i / 32.
+// With many rows the search for a later row to the same place is what costs (every thread looks at every later
+// place), so a caller may lend an int per row of the destination's tile rows: a first pass leaves there, for each
+// place, the last row of x that goes to it (the array starts at -1), and the copy compares instead of searching.
+__global__ void put_last_kernel(const int *__restrict__ ids, int n, int dst_tr, int single, int *__restrict__ last) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int p = ids[(size_t)(i / 32) * 1024 + (i % 32 / 16) * 256 + i % 16];
+  if (p < 0 || p / 32 >= dst_tr) return;
+  atomicMax(last + (single ? 0 : p), i);
+}
+
 template <int FMT>   // BT_BFP8, BT_BFP4, or an item size in bytes (2, 4 coded as -2, -4) for a plain copy
 __global__ void put_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ x, const int *__restrict__ ids, int batch, int n, int tc,
-                           int dst_tr, int x_tr, int single) {
+                           int dst_tr, int x_tr, int single, const int *__restrict__ last) {
   const size_t unit = (size_t)blockIdx.x * blockDim.x + threadIdx.x;          // ((b * n + i) * tc + j) * 2 + f
   if (unit >= (size_t)batch * n * tc * 2) return;
   const int f = (int)(unit % 2), j = (int)(unit / 2 % tc), i = (int)(unit / 2 / tc % n), b = (int)(unit / 2 / tc / n);
   auto place = [&](int r) { return ids[(size_t)(r / 32) * 1024 + (r % 32 / 16) * 256 + r % 16]; };
   const int p = place(i);
   if (p < 0 || p / 32 >= dst_tr) return;
-  for (int later = i + 1; later < n; later++) {
-    const int q = place(later);
-    if (single ? (unsigned)q < 32u : q == p) return;
+  if (last) {
+    if (last[single ? 0 : p] != i) return;
+  } else {
+    for (int later = i + 1; later < n; later++) {
+      const int q = place(later);
+      if (single ? (unsigned)q < 32u : q == p) return;
+    }
   }
   constexpr int ITEM = FMT < 0 ? -FMT : 2;                                    // bytes of a datum of x
   const size_t at_x = (size_t)((i % 32 / 16) * 2 + f) * 256 + (i % 16) * 16;  // first datum of the run in x's tile
@@ -414,7 +429,7 @@ int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles
   return launched("unpack_kernel");
 }
 
-int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batch, int n, int dst_rows, int cols, uint64_t stream) {
+int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batch, int n, int dst_rows, int cols, uint64_t scratch, uint64_t stream) {
   BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4 || fmt == BT_BF16 || fmt == BT_FP32 || fmt == BT_INT32, "bt_put: unknown format %d", fmt);
   BT_REQUIRE(dst && x && ids && dst != x && dst != ids && dst % 16 == 0 && x % 16 == 0, "bt_put: needs 16-byte aligned tensors, x and ids apart from dst");
   if (int s = check_shape("bt_put", batch, n, cols)) return s;
@@ -427,10 +442,17 @@ int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batc
   const uint8_t *s8 = as_ptr<uint8_t>(x);
   const int *places = as_ptr<int>(ids);
   cudaStream_t st = as_stream(stream);
-  if (fmt == BT_BFP8) put_kernel<BT_BFP8><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
-  else if (fmt == BT_BFP4) put_kernel<BT_BFP4><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
-  else if (fmt == BT_BF16) put_kernel<-2><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
-  else put_kernel<-4><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1);
+  int *last = as_ptr<int>(scratch);
+  if (last) {
+    BT_REQUIRE(scratch % 4 == 0, "bt_put: the scratch holds ints");
+    BT_CUDA(cudaMemsetAsync(last, 0xFF, (size_t)dst_tr * 32 * sizeof(int), st));
+    put_last_kernel<<<blocks_for((size_t)n), kThreads, 0, st>>>(places, n, dst_tr, dst_rows == 1, last);
+    if (int s = launched("put_last_kernel")) return s;
+  }
+  if (fmt == BT_BFP8) put_kernel<BT_BFP8><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1, last);
+  else if (fmt == BT_BFP4) put_kernel<BT_BFP4><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1, last);
+  else if (fmt == BT_BF16) put_kernel<-2><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1, last);
+  else put_kernel<-4><<<blocks, kThreads, 0, st>>>(d, s8, places, batch, n, tc, dst_tr, x_tr, dst_rows == 1, last);
   return launched("put_kernel");
 }
 

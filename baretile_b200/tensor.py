@@ -204,7 +204,11 @@ class Tensor:
       self.rt.launch("bt_d2d", (held[-1], t.addr, size), name="copy")
       return held[-1]
     try:
-      self.rt.launch("bt_put", (FMT_CODE[self.dtype], self.addr, apart(x), apart(ids), self.batch, x.rows, self.rows, self.cols), name="put")
+      scratch = 0
+      if x.rows > 64:                       # beyond a few rows: one int per row of the tile rows, to find each place's last row in one pass
+        held.append(self.rt.dram_alloc(4 * 32 * self.tr))
+        scratch = held[-1]
+      self.rt.launch("bt_put", (FMT_CODE[self.dtype], self.addr, apart(x), apart(ids), self.batch, x.rows, self.rows, self.cols, scratch), name="put")
     finally:
       for a in held: self.rt.dram_free(a)
     return self

@@ -99,8 +99,12 @@ int bt_unpack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles
  * rounded exactly as bt_pack_bfp rounds it), else dst's format. ids: an int32 row of n places in tile layout. A
  * place past dst's last tile row is skipped (one in the padding of the last tile row is written there); of several
  * rows to one place the last wins. A dst of one row keeps it in all 32 rows of its tile, as every one-row tensor
- * does. x and ids must not overlap dst: the caller copies an aliased one first (Tensor.put does). */
-int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batch, int n, int dst_rows, int cols, uint64_t stream);
+ * does. x and ids must not overlap dst: the caller copies an aliased one first (Tensor.put does).
+ * scratch: 0, or room for one int per row of dst's tile rows (32 * ceil(dst_rows / 32) ints), used to find the last
+ * row for each place in one pass; without it every row searches all later places, which is fine for a few hundred
+ * rows and quadratic beyond. */
+int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batch, int n, int dst_rows, int cols, uint64_t scratch,
+           uint64_t stream);
 
 /* Tensor.columns() / columns_kernel (baretile/tensor.py:598-611, baretile/kernels.py:1455-1481): a pure
  * byte permutation of a (tile_rows x tile_cols) block-float matrix into the layout the matmul streams.

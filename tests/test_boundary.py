@@ -164,8 +164,8 @@ def test_newer_entry_points_refuse_bad_arguments_before_any_device_work(built):
   with pytest.raises(ValueError, match="w2 goes with"): _lib.call("bt_gemm_bfp", 0, 8, 0, 64, 64, 64, 256, 256, 256, 0, 0, f, 256, 0, 256, 0)
   with pytest.raises(ValueError, match="1 or M rows"): _lib.call("bt_gemm_bfp", 0, 8, 0, 64, 64, 64, 256, 256, 0, 256, 7, f, 256, 0, 256, 0)
   # put: formats, distinct aligned tensors
-  with pytest.raises(ValueError, match="unknown format"): _lib.call("bt_put", 0, 3, 256, 512, 768, 1, 1, 32, 32, 0)
-  with pytest.raises(ValueError, match="apart from dst"): _lib.call("bt_put", 0, 8, 256, 256, 768, 1, 1, 32, 32, 0)
+  with pytest.raises(ValueError, match="unknown format"): _lib.call("bt_put", 0, 3, 256, 512, 768, 1, 1, 32, 32, 0, 0)
+  with pytest.raises(ValueError, match="apart from dst"): _lib.call("bt_put", 0, 8, 256, 256, 768, 1, 1, 32, 32, 0, 0)
   # many small matrices: a table is needed
   with pytest.raises(ValueError, match="no matrices"): _lib.call("bt_tilize_many", 0, 2, 0, None, None, None, None, 0)
   with pytest.raises(ValueError, match="itemsize"): _lib.call("bt_untilize_many", 0, 3, 1, None, None, None, None, 0)

@@ -144,3 +144,23 @@ def test_bad_arguments_raise(rt):
     Tensor.zeros(rt, 64, 32, dtype="bfp8").put(Tensor.zeros(rt, 1, 2, dtype="int32"), Tensor.zeros(rt, 2, 32, dtype="fp32"))
   with pytest.raises(ValueError, match="too many rows"):
     Tensor.zeros(rt, 32, 32).put(Tensor.zeros(rt, 1, 2**16, dtype="int32"), Tensor.zeros(rt, 2**16, 32))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "bfp8"])
+def test_many_rows_with_repeated_places(rt, dtype):
+  # more rows than places, so most places come several times and the last row to each wins: the one-pass search for
+  # each place's last row (used beyond a few rows) against the oracle, which applies the rows in order
+  from baretile_b200.tensor import Tensor
+  rng = np.random.default_rng(28)
+  n, rows = 700, 200
+  x = bf16(rng.normal(0, 1, (2, n, 64)))
+  places = [int(p) for p in rng.integers(-3, rows + 40, n)]            # some negative, some past the last tile row
+  t = Tensor.zeros(rt, rows, 64, batch=2, dtype=dtype)
+  t.put(ids_of(rt, places), upload(rt, x))
+  zero = np.zeros((2 * 7 * 2, o.tile_bytes(dtype)), np.uint8)
+  assert np.array_equal(raw_tiles(rt, t), o.put(zero, places, stored(x, "bf16"), dtype, 2, rows))
+  one = Tensor.zeros(rt, 1, 64, dtype=dtype)                           # a one-row destination: the last row into the tile wins
+  y = bf16(rng.normal(0, 1, (1, 100, 64)))
+  where = [int(p) for p in rng.integers(0, 40, 100)]
+  one.put(ids_of(rt, where), upload(rt, y))
+  assert np.array_equal(raw_tiles(rt, one), o.put(np.zeros((2, o.tile_bytes(dtype)), np.uint8), where, stored(y, "bf16"), dtype, 1, 1))
