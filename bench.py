@@ -524,7 +524,7 @@ def main():
             "clocks": clock,
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                     "ms_per_step": round(e2e_s * 1e3, 3)},
-            "gpu_launches": args.steps * kernels_per_step,
+            "gpu_launches": world * args.steps * kernels_per_step,   # the whole job, like value: every rank launches its own
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 3), "traffic": traffic,
                          "of": peak_kind, "kernel": "gemv_queue_kernel: a step is one launch that runs the 24 matmuls in order; bytes per launch / launch duration averaged over the event-timed region",
                          "per_launch_events_GBps": round(per_launch_sum, 1),
