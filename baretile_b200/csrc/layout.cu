@@ -133,15 +133,32 @@ __device__ __forceinline__ uint32_t pack_run(const uint32_t (&w)[8], uint32_t (&
 #pragma unroll
   for (int k = 0; k < 8; k++) top = max(top, max(w[k] >> 7 & 255u, w[k] >> 23 & 255u));
   uint32_t q[16];
+  if (top >= 9u && top < 255u) {
+    // The same rounding on the multiply-add pipe, which this kernel otherwise leaves idle while the integer pipe is
+    // what bounds it: the magnitude kept is floor(|x| * 2^(133 - top) + 1/2) for bfp8 (2^(129 - top) for bfp4), and
+    // adding 2^23 with rounding toward zero leaves that integer in the low bits. Equal to the integer formula below for
+    // every bf16 pattern whenever the run's largest exponent field is 9..254 (checked exhaustively on the host);
+    // runs of tiny numbers and runs with an infinity or a NaN take the integer formula itself.
+    const float scale = __uint_as_float(((FMT == BT_BFP8 ? 260u : 256u) - top) << 23);
+    constexpr uint32_t kMax = FMT == BT_BFP8 ? 127u : 7u;
 #pragma unroll
-  for (int k = 0; k < 16; k++) {
-    uint32_t b = (w[k / 2] >> (16 * (k % 2))) & 0xFFFFu, e = b >> 7 & 255u, m = (b & 127u) | (e ? 128u : 0u), d = top - e;
-    if (FMT == BT_BFP8) {
-      uint32_t s = min(d, 8u), v = min((m + (1u << s)) >> (s + 1), 127u);
-      q[k] = v ? (b >> 15) << 7 | v : 0u;
-    } else {
-      uint32_t s = min(d, 4u), v = d < 4 ? min((m + (16u << s)) >> (s + 5), 7u) : 0u;
-      q[k] = v ? (b >> 15) << 3 | v : 0u;
+    for (int k = 0; k < 16; k++) {
+      const uint32_t bits = k % 2 ? w[k / 2] & 0xFFFF0000u : w[k / 2] << 16;
+      const uint32_t v = min(__float_as_uint(__fadd_rz(fmaf(fabsf(__uint_as_float(bits)), scale, 0.5f), 8388608.f)) & 0xFFu, kMax);
+      const uint32_t sign = FMT == BT_BFP8 ? bits >> 24 & 0x80u : bits >> 28 & 8u;
+      q[k] = v ? sign | v : 0u;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+      uint32_t b = (w[k / 2] >> (16 * (k % 2))) & 0xFFFFu, e = b >> 7 & 255u, m = (b & 127u) | (e ? 128u : 0u), d = top - e;
+      if (FMT == BT_BFP8) {
+        uint32_t s = min(d, 8u), v = min((m + (1u << s)) >> (s + 1), 127u);
+        q[k] = v ? (b >> 15) << 7 | v : 0u;
+      } else {
+        uint32_t s = min(d, 4u), v = d < 4 ? min((m + (16u << s)) >> (s + 5), 7u) : 0u;
+        q[k] = v ? (b >> 15) << 3 | v : 0u;
+      }
     }
   }
   if (FMT == BT_BFP8) {
@@ -275,40 +292,44 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict
 }
 
 // ---- canonical <-> streaming layout ---------------------------------------------------------------------------
-// A block moves one tile row of one run at a time (up to kPanel tiles, contiguous in both layouts) through shared
-// memory: 16-byte pieces in, 16-byte pieces out, each output piece gathered byte by byte through a table of the
-// permutation built once per block, value bytes recoded on the way (stream_layout.cuh). Blocks stride over the
-// matrix, so the table is built once per block and the grid is sized to the GPU.
+// A block moves kRelayRows tile rows of one run at a time (up to kPanel tiles each; contiguous in the streaming layout,
+// one stretch per tile row in the canonical one) through shared memory: 16-byte pieces in, 16-byte pieces out, each
+// output piece gathered byte by byte through a table of the permutation built once per block, value bytes recoded on
+// the way (stream_layout.cuh). Blocks stride over the matrix, so the table is built once per block and the grid is
+// sized to the GPU. (One tile row per round of two barriers left the warps waiting at the barriers most of the time.)
+constexpr int kRelayRows = 8;
 template <int FMT, bool TO_STREAM>
 __global__ void __launch_bounds__(256) relayout_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
   constexpr int TB = tile_bytes(FMT), PIECES = TB / 16;
   __shared__ uint16_t from[TB];                        // from[output byte of a tile] = input byte of the tile
-  __shared__ __align__(16) uint8_t buf[kPanel * TB];
+  __shared__ __align__(16) uint8_t buf[kRelayRows * kPanel * TB];
   for (int c = threadIdx.x; c < TB; c += blockDim.x) {
     if (TO_STREAM) from[stream_pos<FMT>(c)] = (uint16_t)c;
     else from[c] = (uint16_t)stream_pos<FMT>(c);
   }
-  const int runs = (tc + kPanel - 1) / kPanel;
-  const long long groups = (long long)tr * runs;
+  const int runs = (tc + kPanel - 1) / kPanel, bands = (tr + kRelayRows - 1) / kRelayRows;
+  const long long groups = (long long)bands * runs;
   for (long long gi = blockIdx.x; gi < groups; gi += gridDim.x) {
-    const int ti = (int)(gi / runs), run = (int)(gi % runs), tj = run * kPanel, width = min(kPanel, tc - tj);
-    const size_t canonical = ((size_t)ti * tc + tj) * TB, streamed = stream_tile_index(ti, tj, tr, tc) * (size_t)TB;
-    const uint8_t *in = src + (TO_STREAM ? canonical : streamed);
-    uint8_t *out = dst + (TO_STREAM ? streamed : canonical);
-    __syncthreads();                                   // the table is ready; the previous group's reads of buf are over
-    for (int p = threadIdx.x; p < width * PIECES; p += blockDim.x)
-      *reinterpret_cast<uint4 *>(buf + p * 16) = *reinterpret_cast<const uint4 *>(in + (size_t)p * 16);
+    const int ti0 = (int)(gi / runs) * kRelayRows, run = (int)(gi % runs), tj = run * kPanel, width = min(kPanel, tc - tj), rows = min(kRelayRows, tr - ti0);
+    const size_t streamed = stream_tile_index(ti0, tj, tr, tc) * (size_t)TB;         // the band's tiles follow one another here
+    auto canonical = [&](int t) { return ((size_t)(ti0 + t / width) * tc + tj + t % width) * TB; };   // tile t of the band (row by row) there
+    const int pieces = rows * width * PIECES;
+    __syncthreads();                                   // the table is ready; the previous band's reads of buf are over
+    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
+      const int t = p / PIECES, at = p % PIECES * 16;
+      *reinterpret_cast<uint4 *>(buf + t * TB + at) = *reinterpret_cast<const uint4 *>(src + (TO_STREAM ? canonical(t) : streamed + (size_t)t * TB) + at);
+    }
     __syncthreads();
-    for (int p = threadIdx.x; p < width * PIECES; p += blockDim.x) {
-      const int tile = p / PIECES, first = p % PIECES * 16;
+    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
+      const int t = p / PIECES, first = p % PIECES * 16;
       uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
       for (int k = 0; k < 16; k++) {
-        uint32_t b = buf[tile * TB + from[first + k]];
+        uint32_t b = buf[t * TB + from[first + k]];
         if (first >= 64) b = TO_STREAM ? stream_code<FMT>(b) : canonical_code<FMT>(b);   // a piece is all exponents or all values
         w[k / 4] |= b << (8 * (k % 4));
       }
-      *reinterpret_cast<uint4 *>(out + (size_t)p * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4 *>(dst + (TO_STREAM ? streamed + (size_t)t * TB : canonical(t)) + first) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -464,8 +485,8 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
   if (int s = use_device(device)) return s;
   int sms = 0;
   BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  const long long groups = (long long)tile_rows * ((tile_cols + kPanel - 1) / kPanel);
-  const unsigned blocks = (unsigned)min(groups, (long long)sms * 8);
+  const long long groups = (long long)((tile_rows + kRelayRows - 1) / kRelayRows) * ((tile_cols + kPanel - 1) / kPanel);
+  const unsigned blocks = (unsigned)min(groups, (long long)sms * 6);
   cudaStream_t st = as_stream(stream);
   const uint8_t *s8 = as_ptr<uint8_t>(src);
   uint8_t *d8 = as_ptr<uint8_t>(dst);
