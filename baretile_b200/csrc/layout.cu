@@ -323,11 +323,40 @@ __global__ void __launch_bounds__(256) relayout_kernel(const uint8_t *__restrict
     for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
       const int t = p / PIECES, first = p % PIECES * 16;
       uint32_t w[4] = {0, 0, 0, 0};
+      if (TO_STREAM && first >= 64) {
+        // A piece of values on the way to the streaming layout (the direction every weight takes once): where its 16
+        // bytes come from follows from the layout (stream_pos read backwards), so no table; for bfp8 the two channels
+        // of a lane are neighbours in the canonical tile and load as one 16-bit word; the bytes of a word hold k + 0,
+        // k + 2, k + 1, k + 3; and the recoding takes a word at a time.
+        const uint8_t *tile = buf + t * TB + 64;
+        if (FMT == BT_BFP8) {
+          const int o = first - 64, h = o / 512, lane = o % 512 / 16, g = lane >> 2, tl = lane & 3;
 #pragma unroll
-      for (int k = 0; k < 16; k++) {
-        uint32_t b = buf[t * TB + from[first + k]];
-        if (first >= 64) b = TO_STREAM ? stream_code<FMT>(b) : canonical_code<FMT>(b);   // a piece is all exponents or all values
-        w[k / 4] |= b << (8 * (k % 4));
+          for (int fs = 0; fs < 2; fs++) {
+            const uint8_t *rows = tile + (2 * h + fs) * 256 + 4 * tl * 16 + 2 * g;       // datum rows 4t..4t+3 of the face, channels 2g, 2g+1
+            uint32_t pr[4];
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) pr[kk] = *reinterpret_cast<const uint16_t *>(rows + kk * 16);
+            const uint32_t x = pr[0] | pr[2] << 16, y = pr[1] | pr[3] << 16;
+            w[2 * fs] = __byte_perm(x, y, 0x6420), w[2 * fs + 1] = __byte_perm(x, y, 0x7531);
+          }
+        } else {
+          const int lane = (first - 64) / 16, g = lane >> 2, tl = lane & 3;
+#pragma unroll
+          for (int face = 0; face < 4; face++) {
+            const uint8_t *rows = tile + face * 128 + 4 * tl * 8 + g;
+            w[face] = rows[0] | rows[16] << 8 | rows[8] << 16 | rows[24] << 24;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[i] = stream_code_word<FMT>(w[i]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+          uint32_t b = buf[t * TB + from[first + k]];
+          if (first >= 64) b = canonical_code<FMT>(b);                                   // a piece is all exponents or all values
+          w[k / 4] |= b << (8 * (k % 4));
+        }
       }
       *reinterpret_cast<uint4 *>(dst + (TO_STREAM ? streamed + (size_t)t * TB : canonical(t)) + first) = make_uint4(w[0], w[1], w[2], w[3]);
     }

@@ -70,6 +70,22 @@ __host__ __device__ inline uint32_t canonical_code(uint32_t u) {
   return FMT == BT_BFP8 ? from_offset<8>(u) : from_offset<4>(u & 15) | from_offset<4>(u >> 4) << 4;
 }
 
+// The same recoding of four value bytes at once, canonical -> streamed. Per byte (per nibble for bfp4) the result is
+// offset + q for a positive code and offset - q for a negative one, except that "minus zero" becomes 0; no byte's
+// (nibble's) subtraction borrows from its neighbour, since offset - q is never negative, so plain 32-bit arithmetic
+// does for all lanes.
+template <int FMT>
+__host__ __device__ inline uint32_t stream_code_word(uint32_t w) {
+  if (FMT == BT_BFP8) {
+    const uint32_t q = w & 0x7F7F7F7Fu, neg = (w >> 7 & 0x01010101u) * 0xFFu;            // magnitudes; 0xFF where the sign is set
+    const uint32_t nonzero = ((q + 0x7F7F7F7Fu) >> 7 & 0x01010101u) * 0xFFu;             // 0xFF where the magnitude is not 0
+    return ((q | 0x80808080u) & ~neg) | ((0x80808080u - q) & neg & nonzero);
+  }
+  const uint32_t q = w & 0x77777777u, neg = (w >> 3 & 0x11111111u) * 0xFu;
+  const uint32_t nonzero = ((q | q >> 1 | q >> 2) & 0x11111111u) * 0xFu;
+  return ((q | 0x88888888u) & ~neg) | ((0x88888888u - q) & neg & nonzero);
+}
+
 #ifdef __CUDACC__
 // bf16 lanes 2^(e - 64) for two exponent bytes of a lane's exponent word `ew`: bytes 0 and 2 (HI = 0, the lane's
 // first k pair) or bytes 1 and 3 (HI = 1, its second pair). e << 7 is the exponent field, 0x1F80 = 63 << 7 the bias
