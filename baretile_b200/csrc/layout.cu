@@ -285,8 +285,27 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict
     for (int k = 0; k < 16; k++) x[k] = (w[k / 8] >> (4 * (k % 8)) & 15u) << 4;
   }
   uint32_t o[8];
+  if (e >= 7u && e <= 247u) {
+    // The same values on the multiply-add pipe: a magnitude of up to 7 bits times 2^(e - 133) is exact in fp32 and needs
+    // no rounding to bf16, so its upper half IS the normalised bf16 the integer formula builds (equal for every byte
+    // whenever the exponent byte is 7..247, checked exhaustively on the host; outside that range the formula's
+    // exponent wraps or overflows, and the formula itself runs). 0x4B000000 | mag is the float 2^23 + mag.
+    const float scale = __uint_as_float((e - 6u) << 23);
 #pragma unroll
-  for (int k = 0; k < 8; k++) o[k] = decode_bfp(x[2 * k], e) | decode_bfp(x[2 * k + 1], e) << 16;
+    for (int k = 0; k < 8; k++) {
+      uint32_t half[2];
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const uint32_t v = x[2 * k + j], mag = v & 127u;
+        const float f = (__uint_as_float(0x4B000000u | mag) - 8388608.f) * scale;
+        half[j] = mag ? __float_as_uint(f) | (v & 128u) << 24 : (v & 128u ? 0xFF800000u : 0u);   // a signed zero magnitude reads as -inf
+      }
+      o[k] = __byte_perm(half[0], half[1], 0x7632);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; k++) o[k] = decode_bfp(x[2 * k], e) | decode_bfp(x[2 * k + 1], e) << 16;
+  }
   dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
   dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
