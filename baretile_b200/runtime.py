@@ -156,6 +156,7 @@ class Runtime:
       self.work_bytes = size.value
       self.work = self.dram_alloc(self.work_bytes)
       _lib.call("bt_memset", self.device, self.work, 0, self.work_bytes, self.stream)
+      self.flag = self.host_alloc(4)     # page-locked: wait() has the scratch's error word copied here ahead of its one sync
     except BaseException:
       self.close()
       raise
@@ -242,10 +243,14 @@ class Runtime:
     if launch is not None and launch > self.launches:
       raise ValueError(f"launch {launch} was never queued; the last one queued is {self.launches}")
     self.flush()
+    # the word a wait that gave up sets is the first of the scratch: its copy is queued behind the work and arrives with
+    # the one synchronisation (a separate check afterwards costs a second round trip on every wait)
+    _lib.call("bt_d2h", self.device, ctypes.addressof(self.flag), self.work, 4, self.stream)
     _lib.call("bt_stream_sync", self.device, self.stream, int(timeout * 1000))
-    error = ctypes.c_int()
-    _lib.call("bt_gemv_check", self.device, self.work, self.stream, ctypes.byref(error))
-    if error.value: raise RuntimeError(f"a matmul launch gave up on a bounded wait (code {error.value}); its results are unreliable")
+    if int.from_bytes(self.flag.raw, "little", signed=True):
+      error = ctypes.c_int()
+      _lib.call("bt_gemv_check", self.device, self.work, self.stream, ctypes.byref(error))     # reads it again and resets the counters
+      raise RuntimeError(f"a matmul launch gave up on a bounded wait (code {error.value}); its results are unreliable")
 
   def finished(self):
     done = ctypes.c_int()
