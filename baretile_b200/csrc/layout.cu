@@ -129,36 +129,62 @@ __global__ void round_bf16_kernel(const uint32_t *__restrict__ src, uint16_t *__
 // returns the shared exponent.
 template <int FMT>
 __device__ __forceinline__ uint32_t pack_run(const uint32_t (&w)[8], uint32_t (&values)[4]) {
-  uint32_t top = 0;
+  // the largest exponent field of the 16 values: both halves of a word at once
+  uint32_t both = w[0] & 0x7F807F80u;
 #pragma unroll
-  for (int k = 0; k < 8; k++) top = max(top, max(w[k] >> 7 & 255u, w[k] >> 23 & 255u));
-  uint32_t q[16];
+  for (int k = 1; k < 8; k++) both = __vmaxu2(both, w[k] & 0x7F807F80u);
+  const uint32_t top = max(both & 0xFFFFu, both >> 16) >> 7;
   if (top >= 9u && top < 255u) {
-    // The same rounding on the multiply-add pipe, which this kernel otherwise leaves idle while the integer pipe is
-    // what bounds it: the magnitude kept is floor(|x| * 2^(133 - top) + 1/2) for bfp8 (2^(129 - top) for bfp4), and
-    // adding 2^23 with rounding toward zero leaves that integer in the low bits. Equal to the integer formula below for
-    // every bf16 pattern whenever the run's largest exponent field is 9..254 (checked exhaustively on the host);
-    // runs of tiny numbers and runs with an infinity or a NaN take the integer formula itself.
+    // The rounding on the multiply-add pipe, which this kernel otherwise leaves idle while the integer pipe is what
+    // bounds it: the magnitude kept is floor(|x| * 2^(133 - top) + 1/2) for bfp8 (2^(129 - top) for bfp4), and adding
+    // 2^23 with rounding toward zero leaves that integer in the low byte. Equal to the integer formula below for every
+    // bf16 pattern whenever the run's largest exponent field is 9..254 (checked exhaustively on the host); runs of
+    // tiny numbers and runs with an infinity or a NaN take the integer formula itself. What follows the rounding
+    // works on four values to a word: gather the magnitudes, clamp the one that can exceed the format (128 to 127, or 8
+    // to 7), bring the sign bits over, and leave no sign on a zero magnitude (mag + 0x7F sets a byte's top bit exactly
+    // when mag is not 0, and no byte carries into the next).
     const float scale = __uint_as_float(((FMT == BT_BFP8 ? 260u : 256u) - top) << 23);
-    constexpr uint32_t kMax = FMT == BT_BFP8 ? 127u : 7u;
+    uint32_t bytes[4];
 #pragma unroll
-    for (int k = 0; k < 16; k++) {
-      const uint32_t bits = k % 2 ? w[k / 2] & 0xFFFF0000u : w[k / 2] << 16;
-      const uint32_t v = min(__float_as_uint(__fadd_rz(fmaf(fabsf(__uint_as_float(bits)), scale, 0.5f), 8388608.f)) & 0xFFu, kMax);
-      const uint32_t sign = FMT == BT_BFP8 ? bits >> 24 & 0x80u : bits >> 28 & 8u;
-      q[k] = v ? sign | v : 0u;
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < 16; k++) {
-      uint32_t b = (w[k / 2] >> (16 * (k % 2))) & 0xFFFFu, e = b >> 7 & 255u, m = (b & 127u) | (e ? 128u : 0u), d = top - e;
+    for (int i = 0; i < 4; i++) {
+      const uint32_t a = w[2 * i], b = w[2 * i + 1];
+      auto kept = [&](uint32_t bits) { return __float_as_uint(__fadd_rz(fmaf(fabsf(__uint_as_float(bits)), scale, 0.5f), 8388608.f)); };
+      const uint32_t lo = __byte_perm(kept(a << 16), kept(a & 0xFFFF0000u), 0x4040), hi = __byte_perm(kept(b << 16), kept(b & 0xFFFF0000u), 0x4040);
+      uint32_t mag = __byte_perm(lo, hi, 0x5410);
+      const uint32_t sign = __byte_perm(a, b, 0x7531) & 0x80808080u;
       if (FMT == BT_BFP8) {
-        uint32_t s = min(d, 8u), v = min((m + (1u << s)) >> (s + 1), 127u);
-        q[k] = v ? (b >> 15) << 7 | v : 0u;
+        mag -= mag >> 7 & 0x01010101u;
+        bytes[i] = mag | (sign & (mag + 0x7F7F7F7Fu));
       } else {
-        uint32_t s = min(d, 4u), v = d < 4 ? min((m + (16u << s)) >> (s + 5), 7u) : 0u;
-        q[k] = v ? (b >> 15) << 3 | v : 0u;
+        mag -= mag >> 3 & 0x01010101u;
+        bytes[i] = mag | (sign >> 4 & (mag + 0x07070707u));
       }
+    }
+    if (FMT == BT_BFP8) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) values[i] = bytes[i];
+    } else {
+      // four nibbles out of four bytes: b0 | b1 << 4 | b2 << 8 | b3 << 12
+      auto squeeze = [](uint32_t v) {
+        v = (v | v >> 4) & 0x00FF00FFu;
+        return (v | v >> 8) & 0xFFFFu;
+      };
+      values[0] = squeeze(bytes[0]) | squeeze(bytes[1]) << 16;
+      values[1] = squeeze(bytes[2]) | squeeze(bytes[3]) << 16;
+      values[2] = values[3] = 0;
+    }
+    return top;
+  }
+  uint32_t q[16];
+#pragma unroll
+  for (int k = 0; k < 16; k++) {
+    uint32_t b = (w[k / 2] >> (16 * (k % 2))) & 0xFFFFu, e = b >> 7 & 255u, m = (b & 127u) | (e ? 128u : 0u), d = top - e;
+    if (FMT == BT_BFP8) {
+      uint32_t s = min(d, 8u), v = min((m + (1u << s)) >> (s + 1), 127u);
+      q[k] = v ? (b >> 15) << 7 | v : 0u;
+    } else {
+      uint32_t s = min(d, 4u), v = d < 4 ? min((m + (16u << s)) >> (s + 5), 7u) : 0u;
+      q[k] = v ? (b >> 15) << 3 | v : 0u;
     }
   }
   if (FMT == BT_BFP8) {
@@ -272,39 +298,45 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict
   constexpr size_t TB = tile_bytes(FMT);
   const uint8_t *tile = src + i / 64 * TB;
   int r = (int)(i % 64);
-  uint32_t e = tile[r], x[16];
+  // xb: the 16 value bytes, four to a word (bfp4: each nibble moved to the top of a byte of its own)
+  uint32_t e = tile[r], xb[4], o[8];
   if (FMT == BT_BFP8) {
     uint4 v = *reinterpret_cast<const uint4 *>(tile + 64 + r * 16);
-    uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int k = 0; k < 16; k++) x[k] = w[k / 4] >> (8 * (k % 4)) & 255u;
+    xb[0] = v.x, xb[1] = v.y, xb[2] = v.z, xb[3] = v.w;
   } else {
     uint2 v = *reinterpret_cast<const uint2 *>(tile + 64 + r * 8);
-    uint32_t w[2] = {v.x, v.y};
+    const uint32_t w[2] = {v.x, v.y};
 #pragma unroll
-    for (int k = 0; k < 16; k++) x[k] = (w[k / 8] >> (4 * (k % 8)) & 15u) << 4;
+    for (int k = 0; k < 2; k++) {
+      const uint32_t even = (w[k] & 0x0F0F0F0Fu) << 4, odd = w[k] & 0xF0F0F0F0u;
+      xb[2 * k] = __byte_perm(even, odd, 0x5140), xb[2 * k + 1] = __byte_perm(even, odd, 0x7362);
+    }
   }
-  uint32_t o[8];
   if (e >= 7u && e <= 247u) {
     // The same values on the multiply-add pipe: a magnitude of up to 7 bits times 2^(e - 133) is exact in fp32 and needs
     // no rounding to bf16, so its upper half IS the normalised bf16 the integer formula builds (equal for every byte
     // whenever the exponent byte is 7..247, checked exhaustively on the host; outside that range the formula's
-    // exponent wraps or overflows, and the formula itself runs). 0x4B000000 | mag is the float 2^23 + mag.
+    // exponent wraps or overflows, and the formula itself runs). A byte permute puts a magnitude under 0x4B000000, the
+    // float 2^23 + mag. Signs go in two values at a time, and a signed zero magnitude (halfword 0 so far, found
+    // by the carry of + 0x7FFF into bit 15) reads as -inf, 0xFF80 = 0x8000 | (0x8000 - 0x80).
     const float scale = __uint_as_float((e - 6u) << 23);
 #pragma unroll
     for (int k = 0; k < 8; k++) {
-      uint32_t half[2];
-#pragma unroll
-      for (int j = 0; j < 2; j++) {
-        const uint32_t v = x[2 * k + j], mag = v & 127u;
-        const float f = (__uint_as_float(0x4B000000u | mag) - 8388608.f) * scale;
-        half[j] = mag ? __float_as_uint(f) | (v & 128u) << 24 : (v & 128u ? 0xFF800000u : 0u);   // a signed zero magnitude reads as -inf
-      }
-      o[k] = __byte_perm(half[0], half[1], 0x7632);
+      const uint32_t x = xb[k / 2], mags = x & 0x7F7F7F7Fu;
+      const uint32_t a = k % 2 ? __byte_perm(mags, 0x4B000000u, 0x7442) : __byte_perm(mags, 0x4B000000u, 0x7440);
+      const uint32_t b = k % 2 ? __byte_perm(mags, 0x4B000000u, 0x7443) : __byte_perm(mags, 0x4B000000u, 0x7441);
+      const float fa = (__uint_as_float(a) - 8388608.f) * scale, fb = (__uint_as_float(b) - 8388608.f) * scale;
+      const uint32_t both = __byte_perm(__float_as_uint(fa), __float_as_uint(fb), 0x7632);
+      const uint32_t sign = (k % 2 ? __byte_perm(x, 0u, 0x3424) : __byte_perm(x, 0u, 0x1404)) & 0x80008000u;
+      const uint32_t lone = sign & ~(both + 0x7FFF7FFFu);
+      o[k] = both | sign | (lone - (lone >> 8));
     }
   } else {
 #pragma unroll
-    for (int k = 0; k < 8; k++) o[k] = decode_bfp(x[2 * k], e) | decode_bfp(x[2 * k + 1], e) << 16;
+    for (int k = 0; k < 8; k++) {
+      const uint32_t lo = xb[k / 2] >> (16 * (k % 2)) & 255u, hi = xb[k / 2] >> (16 * (k % 2) + 8) & 255u;
+      o[k] = decode_bfp(lo, e) | decode_bfp(hi, e) << 16;
+    }
   }
   dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
   dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
