@@ -414,6 +414,76 @@ __global__ void __launch_bounds__(256) relayout_kernel(const uint8_t *__restrict
   }
 }
 
+// Canonical -> streaming, the direction every weight takes once, without shared memory or barriers. The permutation
+// moves bytes only inside a tile, and inside a tile only between the four datum rows 4t..4t+3 of a face (64
+// contiguous bytes for bfp8, 32 for bfp4) and the pieces of the lanes 4g + t, g = 0..7. So one thread takes the
+// rows 4t..4t+3 of a pair of faces (bfp8) or of all four faces (bfp4) with eight 128-bit loads, transposes them in
+// registers with byte permutes, recodes a word at a time and writes the eight 16-byte pieces of the lanes 4g + t.
+// The thread of datum rows 4t.. also writes the tile's exponent piece t: one word of each face's exponents, its bytes
+// in the order 0, 2, 1, 3. blockIdx.y is the run of tile columns; a thread's unit is (tile of the run, h, t).
+template <int FMT>
+__global__ void __launch_bounds__(256) to_stream_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
+  constexpr int TB = tile_bytes(FMT), UNITS = FMT == BT_BFP8 ? 8 : 4;
+  const int run = blockIdx.y, tj0 = run * kPanel, width = min(kPanel, tc - tj0);
+  const unsigned long long u = (unsigned long long)blockIdx.x * 256 + threadIdx.x;
+  const uint32_t local = (uint32_t)(u / UNITS), v = (uint32_t)(u % UNITS), tl = v % 4;
+  if (local >= (uint32_t)tr * width) return;
+  const uint32_t ti = width == kPanel ? local / kPanel : local / width, tj = tj0 + (local - ti * width);
+  const uint8_t *in = src + ((size_t)ti * tc + tj) * TB;
+  uint8_t *out = dst + ((size_t)run * kPanel * tr + local) * TB;
+  uint4 a[8];
+  if (FMT == BT_BFP8) {
+    const uint8_t *rows = in + 64 + (v / 4) * 512 + tl * 64;                 // face 2h, datum rows 4t..4t+3; face 2h + 1 is 256 further
+#pragma unroll
+    for (int i = 0; i < 8; i++) a[i] = *reinterpret_cast<const uint4 *>(rows + (i / 4) * 256 + (i % 4) * 16);
+  } else {
+    const uint8_t *rows = in + 64 + tl * 32;                                 // face f 128 further each
+#pragma unroll
+    for (int i = 0; i < 8; i++) a[i] = *reinterpret_cast<const uint4 *>(rows + (i / 2) * 128 + (i % 2) * 16);
+  }
+  if (FMT == BT_BFP4 || v < 4) {
+    uint32_t e[4];
+#pragma unroll
+    for (int face = 0; face < 4; face++) e[face] = __byte_perm(*reinterpret_cast<const uint32_t *>(in + face * 16 + tl * 4), 0u, 0x3120);
+    *reinterpret_cast<uint4 *>(out + tl * 16) = make_uint4(e[0], e[1], e[2], e[3]);
+  }
+  // four bytes b of the words r0..r3 (datum rows kk = 0..3) as one word in the order kk = 0, 2, 1, 3: lo takes byte
+  // 2 * PAIR of each, hi byte 2 * PAIR + 1
+  auto gather = [](uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3, bool upper, uint32_t &lo, uint32_t &hi) {
+    const uint32_t x = upper ? __byte_perm(r0, r2, 0x7362) : __byte_perm(r0, r2, 0x5140), y = upper ? __byte_perm(r1, r3, 0x7362) : __byte_perm(r1, r3, 0x5140);
+    lo = stream_code_word<FMT>(__byte_perm(x, y, 0x5410)), hi = stream_code_word<FMT>(__byte_perm(x, y, 0x7632));
+  };
+  if (FMT == BT_BFP8) {
+    uint8_t *pieces = out + 64 + (v / 4) * 512 + tl * 16;                    // the piece of lane 4g + t is g * 64 further
+#pragma unroll
+    for (int m = 0; m < 4; m++) {                                            // word m of a row holds the channels of g = 2m and 2m + 1
+      uint32_t w[2][4];
+#pragma unroll
+      for (int fs = 0; fs < 2; fs++) {
+        const uint32_t r[4] = {(&a[4 * fs].x)[m], (&a[4 * fs + 1].x)[m], (&a[4 * fs + 2].x)[m], (&a[4 * fs + 3].x)[m]};
+        gather(r[0], r[1], r[2], r[3], false, w[0][2 * fs], w[0][2 * fs + 1]);
+        gather(r[0], r[1], r[2], r[3], true, w[1][2 * fs], w[1][2 * fs + 1]);
+      }
+#pragma unroll
+      for (int odd = 0; odd < 2; odd++) *reinterpret_cast<uint4 *>(pieces + (2 * m + odd) * 64) = make_uint4(w[odd][0], w[odd][1], w[odd][2], w[odd][3]);
+    }
+  } else {
+    uint8_t *pieces = out + 64 + tl * 16;
+    uint32_t w[8][4];                                                        // [g][face]
+#pragma unroll
+    for (int face = 0; face < 4; face++)
+#pragma unroll
+      for (int m = 0; m < 2; m++) {                                          // word m of a row holds the bytes of g = 4m..4m+3
+        const uint32_t r0 = m ? a[2 * face].y : a[2 * face].x, r1 = m ? a[2 * face].w : a[2 * face].z;
+        const uint32_t r2 = m ? a[2 * face + 1].y : a[2 * face + 1].x, r3 = m ? a[2 * face + 1].w : a[2 * face + 1].z;
+        gather(r0, r1, r2, r3, false, w[4 * m][face], w[4 * m + 1][face]);
+        gather(r0, r1, r2, r3, true, w[4 * m + 2][face], w[4 * m + 3][face]);
+      }
+#pragma unroll
+    for (int g = 0; g < 8; g++) *reinterpret_cast<uint4 *>(pieces + g * 64) = make_uint4(w[g][0], w[g][1], w[g][2], w[g][3]);
+  }
+}
+
 int check_shape(const char *what, int batch, int rows, int cols) {
   BT_REQUIRE(batch > 0 && rows > 0 && cols > 0, "%s: tensor dimensions must be positive: %d x %d x %d", what, batch, rows, cols);
   return BT_OK;
@@ -570,6 +640,14 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
   cudaStream_t st = as_stream(stream);
   const uint8_t *s8 = as_ptr<uint8_t>(src);
   uint8_t *d8 = as_ptr<uint8_t>(dst);
+  const int runs = (tile_cols + kPanel - 1) / kPanel;
+  if (to_stream && runs <= 65535) {
+    const unsigned long long units = (unsigned long long)tile_rows * min(kPanel, tile_cols) * (fmt == BT_BFP8 ? 8 : 4);
+    const dim3 grid((unsigned)((units + 255) / 256), (unsigned)runs);
+    if (fmt == BT_BFP8) to_stream_kernel<BT_BFP8><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+    else to_stream_kernel<BT_BFP4><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+    return launched("to_stream_kernel");
+  }
   if (fmt == BT_BFP8 && to_stream) relayout_kernel<BT_BFP8, true><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
   else if (fmt == BT_BFP8) relayout_kernel<BT_BFP8, false><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
   else if (to_stream) relayout_kernel<BT_BFP4, true><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);

@@ -71,19 +71,24 @@ __host__ __device__ inline uint32_t canonical_code(uint32_t u) {
 }
 
 // The same recoding of four value bytes at once, canonical -> streamed. Per byte (per nibble for bfp4) the result is
-// offset + q for a positive code and offset - q for a negative one, except that "minus zero" becomes 0; no byte's
-// (nibble's) subtraction borrows from its neighbour, since offset - q is never negative, so plain 32-bit arithmetic
-// does for all lanes.
+// offset + q for a positive code and, for a negative one, (offset - q) without its top bit: offset - q for q = 1..,
+// and 0 for "minus zero". No byte's (nibble's) subtraction borrows from its neighbour, since offset - q is never
+// negative, so plain 32-bit arithmetic does for all lanes. `neg` is all ones in the bytes (nibbles) whose sign is set;
+// on the device one byte permute in its sign-replicating form makes it.
 template <int FMT>
 __host__ __device__ inline uint32_t stream_code_word(uint32_t w) {
   if (FMT == BT_BFP8) {
-    const uint32_t q = w & 0x7F7F7F7Fu, neg = (w >> 7 & 0x01010101u) * 0xFFu;            // magnitudes; 0xFF where the sign is set
-    const uint32_t nonzero = ((q + 0x7F7F7F7Fu) >> 7 & 0x01010101u) * 0xFFu;             // 0xFF where the magnitude is not 0
-    return ((q | 0x80808080u) & ~neg) | ((0x80808080u - q) & neg & nonzero);
+    const uint32_t q = w & 0x7F7F7F7Fu;
+    uint32_t neg;
+#ifdef __CUDA_ARCH__
+    asm("prmt.b32 %0, %1, 0, 0xBA98;" : "=r"(neg) : "r"(w));
+#else
+    neg = (w >> 7 & 0x01010101u) * 0xFFu;
+#endif
+    return ((q | 0x80808080u) & ~neg) | ((0x80808080u - q) & 0x7F7F7F7Fu & neg);
   }
   const uint32_t q = w & 0x77777777u, neg = (w >> 3 & 0x11111111u) * 0xFu;
-  const uint32_t nonzero = ((q | q >> 1 | q >> 2) & 0x11111111u) * 0xFu;
-  return ((q | 0x88888888u) & ~neg) | ((0x88888888u - q) & neg & nonzero);
+  return ((q | 0x88888888u) & ~neg) | ((0x88888888u - q) & 0x77777777u & neg);
 }
 
 #ifdef __CUDACC__

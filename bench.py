@@ -427,7 +427,7 @@ def main():
       streamed = [Tensor(rt, k, n, dtype=fmt) for _ in range(3)]
       code = int(fmt[3])
       time_kernel(f"pack_kernel<{fmt}>", 2 + tb, [lambda t=t, q=q: rt.launch("bt_pack_bfp", (code, t.addr, q.addr, t.tiles), name=fmt) for t, q in zip(tiles, packed)])
-      time_kernel(f"relayout_kernel<{fmt}>", 2 * tb, [lambda q=q, z=z: rt.launch("bt_relayout", (code, 1, q.tr, q.tc, q.addr, z.addr), name="columns") for q, z in zip(packed, streamed)])
+      time_kernel(f"to_stream_kernel<{fmt}>", 2 * tb, [lambda q=q, z=z: rt.launch("bt_relayout", (code, 1, q.tr, q.tc, q.addr, z.addr), name="columns") for q, z in zip(packed, streamed)])
       time_kernel(f"unpack_kernel<{fmt}>", 2 + tb, [lambda t=t, q=q: rt.launch("bt_unpack_bfp", (code, q.addr, t.addr, t.tiles), name="storage") for t, q in zip(tiles, packed)])
       del packed, streamed
     for f in flats: rt.dram_free(f)

@@ -99,6 +99,31 @@ def test_columns_is_a_permutation_that_reads_back(rt, fmt, shape):
   assert np.array_equal(raw_tiles(rt, c.cast("bf16")), raw_tiles(rt, t.cast("bf16")))
 
 
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("tiles", [(1, 1), (3, 5), (2, 8), (5, 3), (17, 6)])
+def test_relayout_of_arbitrary_bytes(rt, fmt, tiles):
+  # every byte value in every kind of place, the "minus zero" codes a packer never writes included: to the streaming
+  # layout as the oracle lays it out, and back to the very bytes
+  from baretile_b200 import _lib
+  from baretile_b200.tensix import tile_bytes
+  from baretile_b200.tensor import FMT_CODE
+  tr, tc = tiles
+  n = tr * tc * tile_bytes(fmt)
+  raw = np.random.default_rng(tr * 100 + tc).integers(0, 256, n, dtype=np.uint8)
+  raw[:256] = np.arange(256)
+  a, b, c = (rt.dram_alloc(n) for _ in range(3))
+  try:
+    rt.upload(a, raw.tobytes())
+    rt.launch("bt_relayout", (FMT_CODE[fmt], 1, tr, tc, a, b), name="columns")
+    rt.launch("bt_relayout", (FMT_CODE[fmt], 0, tr, tc, b, c), name="columns")
+    rt.wait()
+    streamed = np.frombuffer(rt.download(b, n), np.uint8)
+    assert np.array_equal(streamed, o.to_stream(raw, fmt, tr, tc))
+    assert np.array_equal(np.frombuffer(rt.download(c, n), np.uint8), raw)
+  finally:
+    for addr in (a, b, c): rt.dram_free(addr)
+
+
 def test_bad_arguments_raise(rt):
   from baretile_b200 import _lib
   from baretile_b200.tensor import Tensor
