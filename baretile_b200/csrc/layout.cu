@@ -69,6 +69,50 @@ __global__ void untilize_kernel(const T *__restrict__ src, T *__restrict__ dst, 
   }
 }
 
+// The wide case of both, for matrices of at least 8 tile columns: four half runs to a thread, all four loads issued
+// before the first store (with 16 bytes in flight per thread an SM cannot hold enough threads to keep HBM busy), and no
+// division: blockIdx.x is the tile row, blockIdx.z the matrix of the batch, and blockIdx.y * 1024 + k * 256 +
+// threadIdx.x, k = 0..3, the half run within the tile row.
+template <typename T, bool TILIZE>
+__global__ void __launch_bounds__(kThreads) tile_wide_kernel(const T *__restrict__ src, T *__restrict__ dst, int batch, int rows, int cols, int tr, int tc) {
+  constexpr int W = (int)sizeof(T) * 8 / 16;                           // 16-byte words of a half run
+  const int ti = blockIdx.x;
+  for (int b = blockIdx.z; b < batch; b += gridDim.z)
+    for (int chunk = blockIdx.y; chunk * 1024 < tc * 128; chunk += gridDim.y) {
+      uint4 v[4][W];
+      const uint4 *from[4];
+      uint4 *to[4];
+      bool read[4], write[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int x = chunk * 1024 + k * kThreads + threadIdx.x, tj = x >> 7, h = x & 127, face = h / 32, r16 = h % 32 / 2, c8 = h % 2 * 8;
+        int r = ti * 32 + face / 2 * 16 + r16;
+        const int c0 = tj * 32 + face % 2 * 16 + c8;
+        if (TILIZE && rows == 1) r = 0;                                // a single row fills its tile
+        const bool inside = tj < tc, there = inside && r < rows && c0 < cols;
+        const size_t rowmajor = ((size_t)b * rows + (there ? r : 0)) * cols + (there ? c0 : 0), tiled = (((size_t)b * tr + ti) * tc + (inside ? tj : 0)) * 1024 + h * 8;
+        from[k] = reinterpret_cast<const uint4 *>(src + (TILIZE ? rowmajor : tiled));
+        to[k] = reinterpret_cast<uint4 *>(dst + (TILIZE ? tiled : rowmajor));
+        read[k] = there, write[k] = TILIZE ? inside : there;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+#pragma unroll
+        for (int j = 0; j < W; j++) v[k][j] = read[k] ? from[k][j] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+        if (write[k]) {
+#pragma unroll
+          for (int j = 0; j < W; j++) to[k][j] = v[k][j];
+        }
+    }
+}
+template <typename T, bool TILIZE>
+void launch_tile_wide(const T *src, T *dst, int batch, int rows, int cols, int tr, int tc, cudaStream_t st) {
+  const dim3 grid((unsigned)tr, (unsigned)min((tc * 128 + 1023) / 1024, 65535), (unsigned)min(batch, 65535));
+  tile_wide_kernel<T, TILIZE><<<grid, kThreads, 0, st>>>(src, dst, batch, rows, cols, tr, tc);
+}
+
 // Many small matrices in one launch (a decode step's inputs on their way in, its results on their way out): the table
 // travels by value with the launch, item k owns the half runs [first[k], first[k + 1]), and each thread does what a
 // thread of tilize_kernel / untilize_kernel does for one matrix (batch 1). One launch instead of one per matrix: for
@@ -503,6 +547,11 @@ int bt_tilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch, i
   const bool wide = cols % 8 == 0 && src % 16 == 0 && dst % 16 == 0;
   const unsigned blocks = blocks_for(items);
   cudaStream_t st = as_stream(stream);
+  if (wide && tc >= 8) {
+    if (itemsize == 2) launch_tile_wide<uint16_t, true>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc, st);
+    else launch_tile_wide<uint32_t, true>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc, st);
+    return launched("tile_wide_kernel");
+  }
   if (itemsize == 2) {
     if (wide) tilize_kernel<uint16_t, true><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
     else tilize_kernel<uint16_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
@@ -523,6 +572,11 @@ int bt_untilize(int device, int itemsize, uint64_t src, uint64_t dst, int batch,
   const bool wide = cols % 8 == 0 && src % 16 == 0 && dst % 16 == 0;
   const unsigned blocks = blocks_for(items);
   cudaStream_t st = as_stream(stream);
+  if (wide && tc >= 8) {
+    if (itemsize == 2) launch_tile_wide<uint16_t, false>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc, st);
+    else launch_tile_wide<uint32_t, false>(as_ptr<uint32_t>(src), as_ptr<uint32_t>(dst), batch, rows, cols, tr, tc, st);
+    return launched("tile_wide_kernel");
+  }
   if (itemsize == 2) {
     if (wide) untilize_kernel<uint16_t, true><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);
     else untilize_kernel<uint16_t, false><<<blocks, kThreads, 0, st>>>(as_ptr<uint16_t>(src), as_ptr<uint16_t>(dst), batch, rows, cols, tr, tc);

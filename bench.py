@@ -417,7 +417,7 @@ def main():
       kms = timed(lambda: [fn() for fn in launches], reps) / (reps * len(launches))
       gbps = bytes_per_value * values / (kms * 1e-3) / 1e9
       byte_kernels.append({"kernel": name, "bytes_per_value": bytes_per_value, "us": round(kms * 1e3, 1), "GBps": round(gbps, 1), "frac": round(gbps / peak, 3)})
-    time_kernel("tilize_kernel<bf16>", 4.0, [lambda f=f, t=t: rt.launch("bt_tilize", (2, f, t.addr, 1, k, n), name="upload") for f, t in zip(flats, tiles)])
+    time_kernel("tile_wide_kernel<bf16, tilize>", 4.0, [lambda f=f, t=t: rt.launch("bt_tilize", (2, f, t.addr, 1, k, n), name="upload") for f, t in zip(flats, tiles)])
     for t, bits in zip(tiles, range(3)): rt.launch("bt_tilize", (2, flats[0], t.addr, 1, k, n), name="upload")
     real = Tensor.frombytes(rt, k, n, rounded(rng, (k, n), 0.02, True).tobytes())
     for t in tiles: rt.launch("bt_d2d", (t.addr, real.addr, 2 * values), name="copy")
