@@ -243,20 +243,31 @@ __device__ __forceinline__ uint32_t pack_run(const uint32_t (&w)[8], uint32_t (&
   return top;
 }
 
+// A thread packs two neighbouring runs: 64 bytes in with four 128-bit loads, the two exponents as one 16-bit store,
+// the values as 32 (bfp8) or 16 (bfp4) bytes. (A tile has 64 runs, so a pair never straddles two tiles.)
 template <int FMT>
-__global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__ dst, size_t runs) {
+__global__ void pack_kernel(const uint4 *__restrict__ src, uint8_t *__restrict__ dst, size_t pairs) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= runs) return;
-  uint4 lo = src[2 * i], hi = src[2 * i + 1];
-  const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-  uint32_t v[4];
-  const uint32_t top = pack_run<FMT>(w, v);
+  if (i >= pairs) return;
+  uint4 q[4];
+#pragma unroll
+  for (int k = 0; k < 4; k++) q[k] = src[4 * i + k];
+  uint32_t v[2][4], top[2];
+#pragma unroll
+  for (int k = 0; k < 2; k++) {
+    const uint32_t w[8] = {q[2 * k].x, q[2 * k].y, q[2 * k].z, q[2 * k].w, q[2 * k + 1].x, q[2 * k + 1].y, q[2 * k + 1].z, q[2 * k + 1].w};
+    top[k] = pack_run<FMT>(w, v[k]);
+  }
   constexpr size_t TB = tile_bytes(FMT);
-  uint8_t *tile = dst + i / 64 * TB;
-  int r = (int)(i % 64);
-  tile[r] = (uint8_t)top;
-  if (FMT == BT_BFP8) *reinterpret_cast<uint4 *>(tile + 64 + r * 16) = make_uint4(v[0], v[1], v[2], v[3]);
-  else *reinterpret_cast<uint2 *>(tile + 64 + r * 8) = make_uint2(v[0], v[1]);
+  uint8_t *tile = dst + i / 32 * TB;
+  int r = (int)(i % 32) * 2;
+  *reinterpret_cast<uint16_t *>(tile + r) = (uint16_t)(top[0] | top[1] << 8);
+  if (FMT == BT_BFP8) {
+#pragma unroll
+    for (int k = 0; k < 2; k++) *reinterpret_cast<uint4 *>(tile + 64 + (r + k) * 16) = make_uint4(v[k][0], v[k][1], v[k][2], v[k][3]);
+  } else {
+    *reinterpret_cast<uint4 *>(tile + 64 + r * 8) = make_uint4(v[0][0], v[0][1], v[1][0], v[1][1]);
+  }
 }
 
 // ---- put: rows of x into rows of a tensor, in place (the packer's other user: a block-float KV cache) ----------
@@ -335,34 +346,18 @@ __device__ __forceinline__ uint32_t decode_bfp(uint32_t x, uint32_t e) {
   return (x >> 7) << 15 | ((e - s) & 255u) << 7 | ((m << s) & 0x7Eu);
 }
 
-template <int FMT>
-__global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict__ dst, size_t runs) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= runs) return;
-  constexpr size_t TB = tile_bytes(FMT);
-  const uint8_t *tile = src + i / 64 * TB;
-  int r = (int)(i % 64);
-  // xb: the 16 value bytes, four to a word (bfp4: each nibble moved to the top of a byte of its own)
-  uint32_t e = tile[r], xb[4], o[8];
-  if (FMT == BT_BFP8) {
-    uint4 v = *reinterpret_cast<const uint4 *>(tile + 64 + r * 16);
-    xb[0] = v.x, xb[1] = v.y, xb[2] = v.z, xb[3] = v.w;
-  } else {
-    uint2 v = *reinterpret_cast<const uint2 *>(tile + 64 + r * 8);
-    const uint32_t w[2] = {v.x, v.y};
-#pragma unroll
-    for (int k = 0; k < 2; k++) {
-      const uint32_t even = (w[k] & 0x0F0F0F0Fu) << 4, odd = w[k] & 0xF0F0F0F0u;
-      xb[2 * k] = __byte_perm(even, odd, 0x5140), xb[2 * k + 1] = __byte_perm(even, odd, 0x7362);
-    }
-  }
+// One run: the exponent byte e and the 16 value bytes in xb, four to a word (bfp4: each nibble moved to the top of a
+// byte of its own), to 16 bf16 values in o, two to a word.
+__device__ __forceinline__ void unpack_run(uint32_t e, const uint32_t (&xb)[4], uint32_t (&o)[8]) {
   if (e >= 7u && e <= 247u) {
     // The same values on the multiply-add pipe: a magnitude of up to 7 bits times 2^(e - 133) is exact in fp32 and needs
     // no rounding to bf16, so its upper half IS the normalised bf16 the integer formula builds (equal for every byte
     // whenever the exponent byte is 7..247, checked exhaustively on the host; outside that range the formula's
     // exponent wraps or overflows, and the formula itself runs). A byte permute puts a magnitude under 0x4B000000, the
     // float 2^23 + mag. Signs go in two values at a time, and a signed zero magnitude (halfword 0 so far, found
-    // by the carry of + 0x7FFF into bit 15) reads as -inf, 0xFF80 = 0x8000 | (0x8000 - 0x80).
+    // by the carry of + 0x7FFF into bit 15) reads as -inf, 0xFF80 = 0x8000 | (0x8000 - 0x80). (Asking the run first
+    // whether it has a signed zero at all, which a packer never writes, and filling in only then, was slower: the
+    // branch costs more than the four operations per pair it saves.)
     const float scale = __uint_as_float((e - 6u) << 23);
 #pragma unroll
     for (int k = 0; k < 8; k++) {
@@ -382,6 +377,31 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict
       o[k] = decode_bfp(lo, e) | decode_bfp(hi, e) << 16;
     }
   }
+}
+
+// A thread unpacks one run: 64 consecutive bytes of a warp's output per store instruction pair (two runs to a thread,
+// which serves the packer well, spreads a warp's stores over twice the lines and was slower here).
+template <int FMT>
+__global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict__ dst, size_t runs) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= runs) return;
+  constexpr size_t TB = tile_bytes(FMT);
+  const uint8_t *tile = src + i / 64 * TB;
+  int r = (int)(i % 64);
+  uint32_t e = tile[r], xb[4], o[8];
+  if (FMT == BT_BFP8) {
+    uint4 v = *reinterpret_cast<const uint4 *>(tile + 64 + r * 16);
+    xb[0] = v.x, xb[1] = v.y, xb[2] = v.z, xb[3] = v.w;
+  } else {
+    uint2 v = *reinterpret_cast<const uint2 *>(tile + 64 + r * 8);
+    const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+      const uint32_t even = (w[k] & 0x0F0F0F0Fu) << 4, odd = w[k] & 0xF0F0F0F0u;
+      xb[2 * k] = __byte_perm(even, odd, 0x5140), xb[2 * k + 1] = __byte_perm(even, odd, 0x7362);
+    }
+  }
+  unpack_run(e, xb, o);
   dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
   dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
@@ -637,9 +657,9 @@ int bt_pack_bfp(int device, int fmt, uint64_t src, uint64_t dst, size_t ntiles, 
   BT_REQUIRE(src && dst && ntiles, "bt_pack_bfp: null device address or zero tiles");
   BT_REQUIRE(src % 16 == 0 && dst % 16 == 0, "bt_pack_bfp: tiles must be 16-byte aligned");
   if (int s = use_device(device)) return s;
-  size_t runs = ntiles * 64;
-  if (fmt == BT_BFP8) pack_kernel<BT_BFP8><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint4>(src), as_ptr<uint8_t>(dst), runs);
-  else pack_kernel<BT_BFP4><<<blocks_for(runs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint4>(src), as_ptr<uint8_t>(dst), runs);
+  size_t pairs = ntiles * 32;
+  if (fmt == BT_BFP8) pack_kernel<BT_BFP8><<<blocks_for(pairs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint4>(src), as_ptr<uint8_t>(dst), pairs);
+  else pack_kernel<BT_BFP4><<<blocks_for(pairs), kThreads, 0, as_stream(stream)>>>(as_ptr<uint4>(src), as_ptr<uint8_t>(dst), pairs);
   return launched("pack_kernel");
 }
 
