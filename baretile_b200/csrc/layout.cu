@@ -354,21 +354,21 @@ __device__ __forceinline__ void unpack_run(uint32_t e, const uint32_t (&xb)[4], 
     // no rounding to bf16, so its upper half IS the normalised bf16 the integer formula builds (equal for every byte
     // whenever the exponent byte is 7..247, checked exhaustively on the host; outside that range the formula's
     // exponent wraps or overflows, and the formula itself runs). A byte permute puts a magnitude under 0x4B000000, the
-    // float 2^23 + mag. Signs go in two values at a time, and a signed zero magnitude (halfword 0 so far, found
-    // by the carry of + 0x7FFF into bit 15) reads as -inf, 0xFF80 = 0x8000 | (0x8000 - 0x80). (Asking the run first
-    // whether it has a signed zero at all, which a packer never writes, and filling in only then, was slower: the
-    // branch costs more than the four operations per pair it saves.)
+    // float 2^23 + mag. What a sign adds is worked out four values to a word: `top`, the upper byte of a value's bf16,
+    // gets 0x80 for a negative value and 0xFF for a signed zero magnitude, which reads as -inf, 0xFF80; `low`, the
+    // lower byte, 0x80 for a signed zero (mag + 0x7F sets a byte's top bit exactly when mag is not 0); one byte permute
+    // per pair of values interleaves them. (Asking the run first whether it has a signed zero at all, which a packer
+    // never writes, and filling in only then, was slower: the branch costs more than the operations it saves.)
     const float scale = __uint_as_float((e - 6u) << 23);
 #pragma unroll
     for (int k = 0; k < 8; k++) {
       const uint32_t x = xb[k / 2], mags = x & 0x7F7F7F7Fu;
+      const uint32_t low = x & ~(mags + 0x7F7F7F7Fu) & 0x80808080u, top = (x & 0x80808080u) | (low - (low >> 7));
       const uint32_t a = k % 2 ? __byte_perm(mags, 0x4B000000u, 0x7442) : __byte_perm(mags, 0x4B000000u, 0x7440);
       const uint32_t b = k % 2 ? __byte_perm(mags, 0x4B000000u, 0x7443) : __byte_perm(mags, 0x4B000000u, 0x7441);
       const float fa = (__uint_as_float(a) - 8388608.f) * scale, fb = (__uint_as_float(b) - 8388608.f) * scale;
       const uint32_t both = __byte_perm(__float_as_uint(fa), __float_as_uint(fb), 0x7632);
-      const uint32_t sign = (k % 2 ? __byte_perm(x, 0u, 0x3424) : __byte_perm(x, 0u, 0x1404)) & 0x80008000u;
-      const uint32_t lone = sign & ~(both + 0x7FFF7FFFu);
-      o[k] = both | sign | (lone - (lone >> 8));
+      o[k] = both | (k % 2 ? __byte_perm(top, low, 0x3726) : __byte_perm(top, low, 0x1504));
     }
   } else {
 #pragma unroll
