@@ -40,6 +40,7 @@ SIGNATURES = {
   "bt_event_destroy": [i32, u64],
   "bt_event_record": [i32, u64, u64],
   "bt_event_elapsed_ms": [i32, u64, u64, ctypes.POINTER(f32)],
+  "bt_stream_wait_event": [i32, u64, u64],
   "bt_graph_begin": [i32, u64],
   "bt_graph_end": [i32, u64, ctypes.POINTER(u64)],
   "bt_graph_launch": [i32, u64, u64],

@@ -163,6 +163,13 @@ int bt_event_record(int device, uint64_t event, uint64_t stream) {
   return BT_OK;
 }
 
+int bt_stream_wait_event(int device, uint64_t stream, uint64_t event) {
+  BT_REQUIRE(event, "bt_stream_wait_event: null event");
+  if (int s = use_device(device)) return s;
+  BT_CUDA(cudaStreamWaitEvent(as_stream(stream), reinterpret_cast<cudaEvent_t>(event), 0));
+  return BT_OK;
+}
+
 int bt_event_elapsed_ms(int device, uint64_t start, uint64_t end, float *ms) {
   BT_REQUIRE(ms, "bt_event_elapsed_ms: null result");
   if (int s = use_device(device)) return s;

@@ -58,6 +58,8 @@ class Recording:
     self.rt.check()
     if self.rt.recording is not None: raise RuntimeError("a recording is already in progress on this runtime")
     self.rt.flush()
+    self.rt.join()
+    self.rt._sides(SIDES)                                   # streams and events are made before the capture starts
     self.first = self.rt.launches
     _lib.call("bt_graph_begin", self.rt.device, self.rt.stream)
     self.outer, self.rt.pending = self.rt.pending, []
@@ -70,6 +72,9 @@ class Recording:
       try:
         if kind is None: self.rt.flush()
       finally:
+        try: self.rt.join()                                  # every branch comes back to the stream before the capture ends
+        except Exception:
+          if kind is None: raise
         self.launches, self.rt.log = self.rt.log, self.outer_log
         if self.outer_log is not None: self.outer_log.extend(self.launches)
         self.rt.pending, self.rt.recording = self.outer, None
@@ -127,6 +132,42 @@ class Queue:
       if self.outer is None: self.rt.pending = None
 
 
+SIDES = 4   # streams a runtime keeps for work that runs beside its own
+
+
+class Beside:
+  """Inside `with rt.beside():` copies (and layout launches) are queued on a stream of their own: they start once
+  everything queued on the runtime before the block is done, and run BESIDE what the runtime queues after the block,
+  until the runtime joins them again: at the next wait(), at the end of a recording, or at join(). Each block gets a
+  stream of its own, so two blocks also run beside one another. This is how the copies of a step's inputs and of the
+  previous step's results cross the bus while the current step computes (the reference's host DMA likewise runs while
+  its dispatcher drains the command ring, baretile/runtime.py:734-771). Matmuls stay on the runtime's own stream: they
+  share its scratch.
+
+      with rt.record() as step:
+        with rt.beside(): rt.upload_async(next_in, host_in)        # the next step's inputs
+        with rt.beside(): rt.download_async(host_out, last_out)    # the last step's results
+        ...                                                        # this step's launches
+  """
+  def __init__(self, rt): self.rt = rt
+  def __enter__(self):
+    rt = self.rt
+    rt.check()
+    if rt.side is not None: raise RuntimeError("a beside block is already open on this runtime")
+    rt.flush()
+    if len(rt.unjoined) >= SIDES: raise RuntimeError(f"at most {SIDES} beside blocks between two joins")
+    stream, fork, done = rt._sides(len(rt.unjoined) + 1)[len(rt.unjoined)]
+    _lib.call("bt_event_record", rt.device, fork, rt.stream)
+    _lib.call("bt_stream_wait_event", rt.device, stream, fork)
+    self.done, rt.side, rt.stream = done, rt.stream, stream
+    return self
+  def __exit__(self, *_):
+    rt = self.rt
+    stream, rt.stream, rt.side = rt.stream, rt.side, None
+    _lib.call("bt_event_record", rt.device, self.done, stream)
+    rt.unjoined.append(self.done)
+
+
 class Runtime:
   """Run kernels on one CUDA device, in order. A new Runtime on a chip closes the chip's older runtime, as an
   overlapping rectangle does in the reference (baretile/runtime.py:593-598). Close a runtime to release its
@@ -144,6 +185,7 @@ class Runtime:
     self.log = None
     self.pending = None      # matmuls collected for one queue launch (a list while queueing)
     self.recording = None    # the Recording in progress, which keeps what is freed meanwhile
+    self.sides, self.unjoined, self.side = [], [], None   # (stream, fork event, done event) of beside blocks; their done events not yet joined; the own stream while a block is open
     self.stream = ctypes.c_uint64()
     for other in list(chip.taken.values()): other.close()
     _lib.call("bt_stream_create", self.device, ctypes.byref(self.stream))
@@ -176,6 +218,13 @@ class Runtime:
       for e in (start, end):
         if e: _lib.lib().bt_event_destroy(self.device, e)
     self.sent.clear()
+    if self.side is not None: self.stream, self.side = self.side, None
+    for stream, fork, done in self.sides:
+      try: _lib.call("bt_stream_sync", self.device, stream, 2000)
+      except (TimeoutError, RuntimeError): pass
+      _lib.lib().bt_stream_destroy(self.device, stream)
+      for e in (fork, done): _lib.lib().bt_event_destroy(self.device, e)
+    self.sides, self.unjoined = [], []
     for ptr in getattr(self, "pinned", []): _lib.lib().bt_host_free(ptr)
     self.pinned = []
     for addr, _ in self.arenas: _lib.lib().bt_free(self.device, addr)
@@ -199,6 +248,8 @@ class Runtime:
     is accepted for parity; the entry point sizes its own grid."""
     self.check()
     if units is not None and not 1 <= int(units) < 2**32: raise ValueError("launch units must be in [1, 2**32 - 1]")
+    if self.side is not None and kernel in ("bt_gemv_bfp", "bt_gemv_queue", "bt_gemm_bfp"):
+      raise RuntimeError("a matmul uses the runtime's scratch and runs on its own stream, not in a beside block")
     if self.log is not None: self.log.append((kernel, args, units, name))
     if self.pending is not None and kernel == "bt_gemv_bfp":
       self.pending.append(args)
@@ -226,6 +277,23 @@ class Runtime:
 
   def queue(self): return Queue(self)
 
+  def beside(self): return Beside(self)
+
+  def _sides(self, n):
+    """At least n streams for beside blocks, each with the two events that fork it from and join it to the own stream."""
+    while len(self.sides) < n:
+      made = [ctypes.c_uint64() for _ in range(3)]
+      _lib.call("bt_stream_create", self.device, ctypes.byref(made[0]))
+      for e in made[1:]: _lib.call("bt_event_create", self.device, ctypes.byref(e))
+      self.sides.append(tuple(m.value for m in made))
+    return self.sides
+
+  def join(self):
+    """What is queued from here on runs after the work of every beside block so far."""
+    if self.side is not None: raise RuntimeError("join inside a beside block")
+    done, self.unjoined = self.unjoined, []
+    for e in done: _lib.call("bt_stream_wait_event", self.device, self.stream, e)
+
   def flush(self):
     """Send the matmuls collected so far as one queue launch."""
     if not self.pending: return
@@ -243,6 +311,7 @@ class Runtime:
     if launch is not None and launch > self.launches:
       raise ValueError(f"launch {launch} was never queued; the last one queued is {self.launches}")
     self.flush()
+    self.join()
     # the word a wait that gave up sets is the first of the scratch: its copy is queued behind the work and arrives with
     # the one synchronisation (a separate check afterwards costs a second round trip on every wait)
     _lib.call("bt_d2h", self.device, ctypes.addressof(self.flag), self.work, 4, self.stream)

@@ -12,7 +12,9 @@ The metric is achieved HBM GB/s: algorithmic bytes (packed weight tiles + bf16 x
 step's time. `value` is measured with the inputs resident in HBM (the step recorded once and replayed as a CUDA
 graph, timed with CUDA events on the launching stream). `e2e` is the same step through the public Tensor API with
 host buffers: every matmul's activations are copied from page-locked host memory, tilized, multiplied, untilized and
-copied back inside the timed region (recorded once with Runtime.record() and replayed, then waited for). With N > 1 every rank runs the same sweep on its own GPU (weak scaling, no
+copied back inside the timed region (recorded once with Runtime.record() and replayed, then waited for); the copy of
+the next step's inputs and of the previous step's results run beside the step's kernels (Runtime.beside), and the
+same steps one after the other are reported as `e2e.serial_ms_per_step`. With N > 1 every rank runs the same sweep on its own GPU (weak scaling, no
 data-path collective), times are the maximum over ranks, and the sharded configurations that do exchange data are
 measured separately (`config.sharded`).
 
@@ -311,31 +313,67 @@ def main():
     return out, at
   in_at, in_bytes = offsets([c["xh"].nbytes for c in work])
   out_at, out_bytes = offsets([2 * c["m"] * c["n"] for c in work])
-  host_in, host_out = rt.host_alloc(in_bytes), rt.host_alloc(out_bytes)
-  for at, c in zip(in_at, work): ctypes.memmove(ctypes.addressof(host_in) + at, c["xh"].ctypes.data, c["xh"].nbytes)
-  stage_in, stage_out = rt.dram_alloc(in_bytes), rt.dram_alloc(out_bytes)
-  # The step is recorded once (the copies from and to the page-locked buffers, one layout kernel each way and the
-  # queue launch: five nodes) and replayed: what the reference's tensor.jit does for a decode step. The caller writes its inputs into
-  # the page-locked buffer before a replay and reads the results from the other after wait().
-  with rt.record() as e2e_recording:
-    rt.upload_async(stage_in, host_in)
-    rt.layout_many(True, [(stage_in + at, c["x"].addr, c["m"], c["k"]) for c, at in zip(work, in_at)])       # one launch for all x
+  host_in, host_out = [rt.host_alloc(in_bytes) for _ in range(2)], [rt.host_alloc(out_bytes) for _ in range(2)]
+  for buf in host_in:
+    for at, c in zip(in_at, work): ctypes.memmove(ctypes.addressof(buf) + at, c["xh"].ctypes.data, c["xh"].nbytes)
+  stage_in, stage_out = [rt.dram_alloc(in_bytes) for _ in range(2)], [rt.dram_alloc(out_bytes) for _ in range(2)]
+  for addr, n in [(a, in_bytes) for a in stage_in] + [(a, out_bytes) for a in stage_out]: rt.launch("bt_memset", (addr, 0, n), name="zeros")   # the gaps between matrices too
+  def time_steps(step, after=None):
+    """Host wall clock per step over the timed steps (max over ranks); `after` runs once inside the timed region."""
+    for s in range(args.warmup): step(s)
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(args.warmup, args.warmup + args.steps): step(s)
+    if after: after()
+    per_step = (time.perf_counter() - t0) / args.steps
+    if dist is not None:
+      import torch
+      t = torch.tensor([per_step], device="cuda")
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      per_step = t.item()
+    return per_step
+  # One step after the other. The step is recorded once (the copies from and to the page-locked buffers, one layout
+  # kernel each way and the queue launch: five nodes) and replayed: what the reference's tensor.jit does for a decode
+  # step. The caller writes its inputs into the page-locked buffer before a replay and reads the results from the
+  # other after wait().
+  with rt.record() as serial:
+    rt.upload_async(stage_in[0], host_in[0])
+    rt.layout_many(True, [(stage_in[0] + at, c["x"].addr, c["m"], c["k"]) for c, at in zip(work, in_at)])       # one launch for all x
     ys = [expression(c).realize() for c in work]
-    rt.layout_many(False, [(y.addr, stage_out + at, c["m"], c["n"]) for c, y, at in zip(work, ys, out_at)])  # and one for all results
-    rt.download_async(host_out, stage_out)
-  def e2e_step():
-    e2e_recording.replay()
+    rt.layout_many(False, [(y.addr, stage_out[0] + at, c["m"], c["n"]) for c, y, at in zip(work, ys, out_at)])  # and one for all results
+    rt.download_async(host_out[0], stage_out[0])
+  def serial_step(s):
+    serial.replay()
     rt.wait()
-  for _ in range(args.warmup): e2e_step()
-  barrier()
-  t0 = time.perf_counter()
-  for _ in range(args.steps): e2e_step()
-  e2e_s = (time.perf_counter() - t0) / args.steps
-  if dist is not None:
-    import torch
-    t = torch.tensor([e2e_s], device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = t.item()
+  serial_s = time_steps(serial_step)
+  expected = bytes(host_out[0])
+  # The same steps with the bus busy beside the kernels (Runtime.beside): while step s computes on buffer set s % 2, the
+  # inputs of step s + 1 are copied into the other set and the results of step s - 1 are copied out of it. One
+  # recording per set: two branches of one copy each and the step's three launches, replayed in turn and waited for
+  # every step. Every step's inputs cross the bus and every step's results reach the host inside the timed region;
+  # a result is in the caller's hands one step later, and the last one after a copy of its own (timed too).
+  def overlapped(b):
+    with rt.record() as g:
+      with rt.beside(): rt.upload_async(stage_in[1 - b], host_in[1 - b])
+      with rt.beside(): rt.download_async(host_out[1 - b], stage_out[1 - b])
+      rt.layout_many(True, [(stage_in[b] + at, c["x"].addr, c["m"], c["k"]) for c, at in zip(work, in_at)])
+      out = [expression(c).realize() for c in work]
+      rt.layout_many(False, [(y.addr, stage_out[b] + at, c["m"], c["n"]) for c, y, at in zip(work, out, out_at)])
+    return g, out
+  rt.upload_async(stage_in[0], host_in[0])
+  pipe = [overlapped(0), overlapped(1)]
+  rt.wait()
+  for buf in host_out: ctypes.memset(ctypes.addressof(buf), 0, out_bytes)
+  def pipe_step(s):
+    pipe[s % 2][0].replay()
+    rt.wait()
+  def drain():
+    last = (args.warmup + args.steps - 1) % 2
+    rt.download_async(host_out[last], stage_out[last])
+    rt.wait()
+  e2e_s = time_steps(pipe_step, drain)
+  if args.warmup + args.steps >= 2 and any(bytes(buf) != expected for buf in host_out):
+    raise SystemExit("the overlapped end-to-end steps did not return the bytes the step-by-step ones did")
   e2e = world * step_bytes / e2e_s / 1e9
   clock = clocks.stop() if clocks else None
 
@@ -523,7 +561,8 @@ def main():
                        "big": big, "byte_kernels": byte_kernels, "prefill": prefill, "sharded": sharded},
             "clocks": clock,
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                    "ms_per_step": round(e2e_s * 1e3, 3)},
+                    "ms_per_step": round(e2e_s * 1e3, 3), "serial_ms_per_step": round(serial_s * 1e3, 3),
+                    "how": "host wall clock; every step copies its inputs from page-locked memory and its results back; the copies of the next step's inputs and of the previous step's results run beside the step's kernels (Runtime.beside), each step is waited for; serial_ms_per_step is one step after the other"},
             "gpu_launches": world * args.steps * kernels_per_step,   # the whole job, like value: every rank launches its own
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 3), "traffic": traffic,
                          "of": peak_kind, "kernel": "gemv_queue_kernel: a step is one launch that runs the 24 matmuls in order; bytes per launch / launch duration averaged over the event-timed region",

@@ -62,6 +62,12 @@ int bt_event_create(int device, uint64_t *event);      /* dispatcher timestamps 
 int bt_event_destroy(int device, uint64_t event);
 int bt_event_record(int device, uint64_t event, uint64_t stream);
 int bt_event_elapsed_ms(int device, uint64_t start, uint64_t end, float *ms);
+/* What is queued on `stream` after this call runs only once the work recorded by `event` is done; the host does not
+ * wait. With bt_event_record it lets copies on a second stream run beside the kernels of the first (the reference
+ * overlaps its host DMA with running kernels the same way: uploads go through the PCIe window while the dispatcher
+ * drains the command ring, baretile/runtime.py:734-771). Inside bt_graph_begin / bt_graph_end it forks and joins
+ * branches of the recorded graph. */
+int bt_stream_wait_event(int device, uint64_t stream, uint64_t event);
 
 /* ---- replay: tensor.jit / Recording (baretile/tensor.py:1171-1293, baretile/runtime.py:725-732) ----
  * Between bt_graph_begin and bt_graph_end the launches queued on the stream are recorded instead of run;

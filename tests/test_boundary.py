@@ -131,6 +131,7 @@ def test_queue_collects_matmuls_and_flushes_in_order(monkeypatch):
   monkeypatch.setattr(_lib, "call", fake_call)
   rt = runtime.Runtime.__new__(runtime.Runtime)
   rt.active, rt.device, rt.stream, rt.launches, rt.sent, rt.log, rt.pending, rt.timing, rt.work, rt.work_bytes = True, 0, 7, 0, {}, None, None, False, 4096, 1 << 20
+  rt.sides, rt.unjoined, rt.side = [], [], None
   def matmul(x, out, epilogue=0, w2=0, alpha=1.0):
     rt.launch("bt_gemv_bfp", (8, epilogue, 4, 512, 1024, x, 0x1000, w2, 0, ctypes.c_float(alpha), out, 0, 0, 0, 0, rt.work, rt.work_bytes), name="matmul")
   matmul(0x10, 0x20)                                                  # outside a queue: sent at once
@@ -152,6 +153,44 @@ def test_queue_collects_matmuls_and_flushes_in_order(monkeypatch):
       matmul(0x10, 0x20)
       raise KeyError("the block fails")
   assert calls == [] and rt.pending is None                          # a failed block sends nothing
+
+
+def test_beside_blocks_fork_from_the_stream_and_join_it_again(monkeypatch):
+  # host logic of Runtime.beside(): a block's copies go to a stream of its own that starts behind what the runtime has
+  # queued; the runtime's later launches do not wait for it until join(); the C-ABI calls are captured, no device needed
+  from baretile_b200 import _lib, runtime
+  calls, made = [], iter(range(100, 200))
+  def fake_call(name, *args):
+    if name in ("bt_stream_create", "bt_event_create"): args[-1]._obj.value = next(made)
+    calls.append((name, args))
+  monkeypatch.setattr(_lib, "call", fake_call)
+  rt = runtime.Runtime.__new__(runtime.Runtime)
+  rt.active, rt.device, rt.stream, rt.launches, rt.sent, rt.log, rt.pending, rt.timing, rt.work, rt.work_bytes = True, 0, 7, 0, {}, None, None, False, 4096, 1 << 20
+  rt.sides, rt.unjoined, rt.side, rt.recording = [], [], None, None
+  buf = (ctypes.c_char * 64)()
+  with rt.beside(): rt.upload_async(0x1000, buf)
+  with rt.beside(): rt.download_async(buf, 0x2000)
+  rt.launch("bt_untilize", (2, 0x30, 0x40, 1, 4, 1024), name="readback")
+  (s1, f1, d1), (s2, f2, d2) = rt.sides
+  assert len({7, s1, s2}) == 3 and rt.stream == 7 and rt.unjoined == [d1, d2]
+  order = [(n, a) for n, a in calls if n not in ("bt_stream_create", "bt_event_create")]
+  assert [n for n, _ in order] == ["bt_event_record", "bt_stream_wait_event", "bt_h2d", "bt_event_record",
+                                   "bt_event_record", "bt_stream_wait_event", "bt_d2h", "bt_event_record", "bt_untilize"]
+  assert order[0][1] == (0, f1, 7) and order[1][1] == (0, s1, f1) and order[2][1][-1] == s1 and order[3][1] == (0, d1, s1)
+  assert order[4][1] == (0, f2, 7) and order[5][1] == (0, s2, f2) and order[6][1][-1] == s2 and order[7][1] == (0, d2, s2)
+  assert order[8][1][-1] == 7                                         # the runtime's own launch did not wait for either
+  calls.clear()
+  rt.join()
+  assert calls == [("bt_stream_wait_event", (0, 7, d1)), ("bt_stream_wait_event", (0, 7, d2))] and rt.unjoined == []
+  with pytest.raises(RuntimeError, match="own stream"):
+    with rt.beside(): rt.launch("bt_gemv_bfp", (8, 0, 4, 512, 1024, 0x10, 0x1000, 0, 0, ctypes.c_float(1.0), 0x20, 0, 0, 0, 0, rt.work, rt.work_bytes))
+  assert rt.stream == 7 and rt.side is None                           # the failed block gave the stream back
+  rt.join()
+  calls.clear()
+  with rt.beside():
+    with pytest.raises(RuntimeError, match="already open"):
+      with rt.beside(): pass
+    with pytest.raises(RuntimeError, match="inside a beside block"): rt.join()
 
 
 def test_newer_entry_points_refuse_bad_arguments_before_any_device_work(built):

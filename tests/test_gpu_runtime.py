@@ -203,3 +203,56 @@ def test_replay_with_bound_arguments_and_jit(rt):
   fast = jit(f)
   for x, w in zip(xs, want): assert np.array_equal(fast(x).numpy(), w)
   with pytest.raises(ValueError, match="where the first call had"): fast(upload(rt, acts(rng, 5, 512)))
+
+
+def test_copies_beside_a_recorded_step(rt):
+  # Runtime.beside(): while step s computes on buffer set s % 2, the inputs of step s + 1 go into the other set and
+  # the results of step s - 1 come out of it, as branches of the step's recording. Every step has its own input, so a
+  # copy that ran too early or too late shows as a wrong result.
+  import ctypes
+  from helpers import acts, upload, weights
+  from oracle import bfp_oracle as o
+  from baretile_b200.tensor import Tensor
+  rng = np.random.default_rng(77)
+  m, k, n, steps = 4, 512, 1024, 7
+  w = upload(rt, weights(rng, k, n)).cast("bfp8").columns()
+  xs = [acts(rng, m, k) for _ in range(steps)]
+  want = [o.bf16_bits((upload(rt, x) @ w).relu().numpy()).tobytes() for x in xs]
+  host_in, host_out = [rt.host_alloc(m * k * 2) for _ in range(2)], [rt.host_alloc(m * n * 2) for _ in range(2)]
+  stage_in, stage_out = [rt.dram_alloc(m * k * 2) for _ in range(2)], [rt.dram_alloc(m * n * 2) for _ in range(2)]
+  tx = Tensor(rt, m, k)
+  def put(buf, x): ctypes.memmove(ctypes.addressof(buf), o.bf16_bits(x).tobytes(), m * k * 2)
+  def recorded(b):
+    with rt.record() as g:
+      with rt.beside(): rt.upload_async(stage_in[1 - b], host_in[1 - b])
+      with rt.beside(): rt.download_async(host_out[1 - b], stage_out[1 - b])
+      rt.layout_many(True, [(stage_in[b], tx.addr, m, k)])
+      y = (tx @ w).relu().realize()
+      rt.layout_many(False, [(y.addr, stage_out[b], m, n)])
+    assert not rt.unjoined
+    return g, y
+  put(host_in[0], xs[0]); put(host_in[1], xs[0])
+  rt.upload_async(stage_in[0], host_in[0])
+  pipe = [recorded(0), recorded(1)]                                  # each also runs once, on whatever the buffers hold
+  rt.wait()
+  try:
+    rt.upload_async(stage_in[0], host_in[0])
+    for s in range(steps):
+      if s + 1 < steps: put(host_in[(s + 1) % 2], xs[s + 1])          # the caller's part: the next input, before the replay
+      pipe[s % 2][0].replay()
+      rt.wait()
+      if s: assert bytes(host_out[(s - 1) % 2]) == want[s - 1], s      # the previous step's result is here now
+    rt.download_async(host_out[(steps - 1) % 2], stage_out[(steps - 1) % 2])
+    rt.wait()
+    assert bytes(host_out[(steps - 1) % 2]) == want[steps - 1]
+    # outside a recording: a copy beside a long launch, joined by wait()
+    big = rt.dram_alloc(256 << 20)
+    rt.launch("bt_memset", (big, 0, 256 << 20), name="zeros")
+    with rt.beside(): rt.download_async(host_out[0], stage_out[(steps - 1) % 2])
+    assert len(rt.unjoined) == 1
+    rt.wait()
+    assert not rt.unjoined and bytes(host_out[0]) == want[steps - 1]
+    rt.dram_free(big)
+  finally:
+    for g, _ in pipe: g.close()
+    for addr in stage_in + stage_out: rt.dram_free(addr)
