@@ -523,7 +523,7 @@ def main():
                "mlp_ideal_us": round(mlp_bytes / world / peak / 1e3, 1), "head_ideal_us": round(head_bytes / world / peak / 1e3, 1)}
     def median_us(fn):
       for _ in range(5): fn()
-      return round(statistics.median(timed(fn, 10) / 10 for _ in range(4)) * 1e3, 1)   # a median: the first collective of a size may set up connections
+      return round(statistics.median(timed(fn, 10) / 10 for _ in range(7)) * 1e3, 1)   # a median: the first collective of a size may set up connections, and eight ranks' hosts disturb one another
     for m in (1, 4, 16):
       xs = Tensor.frombytes(rt, m, K3, rounded(rng, (m, K3), 1.0).tobytes())
       for gather in (True, False):
