@@ -407,77 +407,6 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ src, uint4 *__restrict
 }
 
 // ---- canonical <-> streaming layout ---------------------------------------------------------------------------
-// A block moves kRelayRows tile rows of one run at a time (up to kPanel tiles each; contiguous in the streaming layout,
-// one stretch per tile row in the canonical one) through shared memory: 16-byte pieces in, 16-byte pieces out, each
-// output piece gathered byte by byte through a table of the permutation built once per block, value bytes recoded on
-// the way (stream_layout.cuh). Blocks stride over the matrix, so the table is built once per block and the grid is
-// sized to the GPU. (One tile row per round of two barriers left the warps waiting at the barriers most of the time.)
-constexpr int kRelayRows = 8;
-template <int FMT, bool TO_STREAM>
-__global__ void __launch_bounds__(256) relayout_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
-  constexpr int TB = tile_bytes(FMT), PIECES = TB / 16;
-  __shared__ uint16_t from[TB];                        // from[output byte of a tile] = input byte of the tile
-  __shared__ __align__(16) uint8_t buf[kRelayRows * kPanel * TB];
-  for (int c = threadIdx.x; c < TB; c += blockDim.x) {
-    if (TO_STREAM) from[stream_pos<FMT>(c)] = (uint16_t)c;
-    else from[c] = (uint16_t)stream_pos<FMT>(c);
-  }
-  const int runs = (tc + kPanel - 1) / kPanel, bands = (tr + kRelayRows - 1) / kRelayRows;
-  const long long groups = (long long)bands * runs;
-  for (long long gi = blockIdx.x; gi < groups; gi += gridDim.x) {
-    const int ti0 = (int)(gi / runs) * kRelayRows, run = (int)(gi % runs), tj = run * kPanel, width = min(kPanel, tc - tj), rows = min(kRelayRows, tr - ti0);
-    const size_t streamed = stream_tile_index(ti0, tj, tr, tc) * (size_t)TB;         // the band's tiles follow one another here
-    auto canonical = [&](int t) { return ((size_t)(ti0 + t / width) * tc + tj + t % width) * TB; };   // tile t of the band (row by row) there
-    const int pieces = rows * width * PIECES;
-    __syncthreads();                                   // the table is ready; the previous band's reads of buf are over
-    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
-      const int t = p / PIECES, at = p % PIECES * 16;
-      *reinterpret_cast<uint4 *>(buf + t * TB + at) = *reinterpret_cast<const uint4 *>(src + (TO_STREAM ? canonical(t) : streamed + (size_t)t * TB) + at);
-    }
-    __syncthreads();
-    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
-      const int t = p / PIECES, first = p % PIECES * 16;
-      uint32_t w[4] = {0, 0, 0, 0};
-      if (TO_STREAM && first >= 64) {
-        // A piece of values on the way to the streaming layout (the direction every weight takes once): where its 16
-        // bytes come from follows from the layout (stream_pos read backwards), so no table; for bfp8 the two channels
-        // of a lane are neighbours in the canonical tile and load as one 16-bit word; the bytes of a word hold k + 0,
-        // k + 2, k + 1, k + 3; and the recoding takes a word at a time.
-        const uint8_t *tile = buf + t * TB + 64;
-        if (FMT == BT_BFP8) {
-          const int o = first - 64, h = o / 512, lane = o % 512 / 16, g = lane >> 2, tl = lane & 3;
-#pragma unroll
-          for (int fs = 0; fs < 2; fs++) {
-            const uint8_t *rows = tile + (2 * h + fs) * 256 + 4 * tl * 16 + 2 * g;       // datum rows 4t..4t+3 of the face, channels 2g, 2g+1
-            uint32_t pr[4];
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++) pr[kk] = *reinterpret_cast<const uint16_t *>(rows + kk * 16);
-            const uint32_t x = pr[0] | pr[2] << 16, y = pr[1] | pr[3] << 16;
-            w[2 * fs] = __byte_perm(x, y, 0x6420), w[2 * fs + 1] = __byte_perm(x, y, 0x7531);
-          }
-        } else {
-          const int lane = (first - 64) / 16, g = lane >> 2, tl = lane & 3;
-#pragma unroll
-          for (int face = 0; face < 4; face++) {
-            const uint8_t *rows = tile + face * 128 + 4 * tl * 8 + g;
-            w[face] = rows[0] | rows[16] << 8 | rows[8] << 16 | rows[24] << 24;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; i++) w[i] = stream_code_word<FMT>(w[i]);
-      } else {
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-          uint32_t b = buf[t * TB + from[first + k]];
-          if (first >= 64) b = canonical_code<FMT>(b);                                   // a piece is all exponents or all values
-          w[k / 4] |= b << (8 * (k % 4));
-        }
-      }
-      *reinterpret_cast<uint4 *>(dst + (TO_STREAM ? streamed + (size_t)t * TB : canonical(t)) + first) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-  }
-}
-
 // Canonical -> streaming, the direction every weight takes once, without shared memory or barriers. The permutation
 // moves bytes only inside a tile, and inside a tile only between the four datum rows 4t..4t+3 of a face (64
 // contiguous bytes for bfp8, 32 for bfp4) and the pieces of the lanes 4g + t, g = 0..7. So one thread takes the
@@ -545,6 +474,63 @@ __global__ void __launch_bounds__(256) to_stream_kernel(const uint8_t *__restric
       }
 #pragma unroll
     for (int g = 0; g < 8; g++) *reinterpret_cast<uint4 *>(pieces + g * 64) = make_uint4(w[g][0], w[g][1], w[g][2], w[g][3]);
+  }
+}
+
+// Streaming -> canonical, the mirror image: the same thread takes the eight pieces of the lanes 4g + t, decodes a word
+// at a time, undoes the transposition and writes the datum rows 4t..4t+3 (and the exponent words of t).
+template <int FMT>
+__global__ void __launch_bounds__(256) from_stream_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int tr, int tc) {
+  constexpr int TB = tile_bytes(FMT), UNITS = FMT == BT_BFP8 ? 8 : 4;
+  const int run = blockIdx.y, tj0 = run * kPanel, width = min(kPanel, tc - tj0);
+  const unsigned long long u = (unsigned long long)blockIdx.x * 256 + threadIdx.x;
+  const uint32_t local = (uint32_t)(u / UNITS), v = (uint32_t)(u % UNITS), tl = v % 4;
+  if (local >= (uint32_t)tr * width) return;
+  const uint32_t ti = width == kPanel ? local / kPanel : local / width, tj = tj0 + (local - ti * width);
+  const uint8_t *in = src + ((size_t)run * kPanel * tr + local) * TB;
+  uint8_t *out = dst + ((size_t)ti * tc + tj) * TB;
+  const uint8_t *pieces = in + 64 + (FMT == BT_BFP8 ? (v / 4) * 512 : 0) + tl * 16;   // the piece of lane 4g + t is g * 64 further
+  uint4 p[8], a[8];
+#pragma unroll
+  for (int g = 0; g < 8; g++) p[g] = *reinterpret_cast<const uint4 *>(pieces + g * 64);
+  if (FMT == BT_BFP4 || v < 4) {
+    const uint4 e = *reinterpret_cast<const uint4 *>(in + tl * 16);
+    const uint32_t w[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+    for (int face = 0; face < 4; face++) *reinterpret_cast<uint32_t *>(out + face * 16 + tl * 4) = __byte_perm(w[face], 0u, 0x3120);
+  }
+  // the inverse of to_stream_kernel's gather: four words that each hold one byte of the datum rows kk = 0, 2, 1, 3
+  // (bytes 0..3 of the rows' word in w0..w3) back to the four rows' words
+  auto scatter = [](uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    w0 = canonical_code_word<FMT>(w0), w1 = canonical_code_word<FMT>(w1), w2 = canonical_code_word<FMT>(w2), w3 = canonical_code_word<FMT>(w3);
+    const uint32_t t = __byte_perm(w0, w1, 0x5140), t2 = __byte_perm(w2, w3, 0x5140), s = __byte_perm(w0, w1, 0x7362), s2 = __byte_perm(w2, w3, 0x7362);
+    r0 = __byte_perm(t, t2, 0x5410), r2 = __byte_perm(t, t2, 0x7632), r1 = __byte_perm(s, s2, 0x5410), r3 = __byte_perm(s, s2, 0x7632);
+  };
+  if (FMT == BT_BFP8) {
+#pragma unroll
+    for (int m = 0; m < 4; m++)                                              // word m of a row holds the channels of g = 2m and 2m + 1
+#pragma unroll
+      for (int fs = 0; fs < 2; fs++) {
+        const uint32_t e0 = fs ? p[2 * m].z : p[2 * m].x, e1 = fs ? p[2 * m].w : p[2 * m].y;
+        const uint32_t o0 = fs ? p[2 * m + 1].z : p[2 * m + 1].x, o1 = fs ? p[2 * m + 1].w : p[2 * m + 1].y;
+        scatter(e0, e1, o0, o1, (&a[4 * fs].x)[m], (&a[4 * fs + 1].x)[m], (&a[4 * fs + 2].x)[m], (&a[4 * fs + 3].x)[m]);
+      }
+    uint8_t *rows = out + 64 + (v / 4) * 512 + tl * 64;                      // face 2h, datum rows 4t..4t+3; face 2h + 1 is 256 further
+#pragma unroll
+    for (int i = 0; i < 8; i++) *reinterpret_cast<uint4 *>(rows + (i / 4) * 256 + (i % 4) * 16) = a[i];
+  } else {
+#pragma unroll
+    for (int face = 0; face < 4; face++)
+#pragma unroll
+      for (int m = 0; m < 2; m++) {                                          // word m of a row holds the bytes of g = 4m..4m+3
+        uint32_t r0, r1, r2, r3;
+        scatter((&p[4 * m].x)[face], (&p[4 * m + 1].x)[face], (&p[4 * m + 2].x)[face], (&p[4 * m + 3].x)[face], r0, r1, r2, r3);
+        if (m == 0) a[2 * face].x = r0, a[2 * face].z = r1, a[2 * face + 1].x = r2, a[2 * face + 1].z = r3;
+        else a[2 * face].y = r0, a[2 * face].w = r1, a[2 * face + 1].y = r2, a[2 * face + 1].w = r3;
+      }
+    uint8_t *rows = out + 64 + tl * 32;                                      // face f 128 further each
+#pragma unroll
+    for (int i = 0; i < 8; i++) *reinterpret_cast<uint4 *>(rows + (i / 2) * 128 + (i % 2) * 16) = a[i];
   }
 }
 
@@ -705,28 +691,20 @@ int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols
   BT_REQUIRE(fmt == BT_BFP8 || fmt == BT_BFP4, "bt_relayout: format must be bfp8 (8) or bfp4 (4), not %d", fmt);
   BT_REQUIRE(tile_rows > 0 && tile_cols > 0, "bt_relayout: tile counts must be positive: %d x %d", tile_rows, tile_cols);
   BT_REQUIRE((long long)tile_rows * tile_cols < (1ll << 31), "bt_relayout: too many tiles for one launch");
+  const int runs = (tile_cols + kPanel - 1) / kPanel;
+  BT_REQUIRE(runs <= 65535, "bt_relayout: at most %d tile columns in one launch, not %d", 65535 * kPanel, tile_cols);
   BT_REQUIRE(src && dst && src != dst && src % 16 == 0 && dst % 16 == 0, "bt_relayout: needs distinct 16-byte aligned buffers");
   if (int s = use_device(device)) return s;
-  int sms = 0;
-  BT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  const long long groups = (long long)((tile_rows + kRelayRows - 1) / kRelayRows) * ((tile_cols + kPanel - 1) / kPanel);
-  const unsigned blocks = (unsigned)min(groups, (long long)sms * 6);
   cudaStream_t st = as_stream(stream);
   const uint8_t *s8 = as_ptr<uint8_t>(src);
   uint8_t *d8 = as_ptr<uint8_t>(dst);
-  const int runs = (tile_cols + kPanel - 1) / kPanel;
-  if (to_stream && runs <= 65535) {
-    const unsigned long long units = (unsigned long long)tile_rows * min(kPanel, tile_cols) * (fmt == BT_BFP8 ? 8 : 4);
-    const dim3 grid((unsigned)((units + 255) / 256), (unsigned)runs);
-    if (fmt == BT_BFP8) to_stream_kernel<BT_BFP8><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
-    else to_stream_kernel<BT_BFP4><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
-    return launched("to_stream_kernel");
-  }
-  if (fmt == BT_BFP8 && to_stream) relayout_kernel<BT_BFP8, true><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  else if (fmt == BT_BFP8) relayout_kernel<BT_BFP8, false><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  else if (to_stream) relayout_kernel<BT_BFP4, true><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  else relayout_kernel<BT_BFP4, false><<<blocks, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
-  return launched("relayout_kernel");
+  const unsigned long long units = (unsigned long long)tile_rows * min(kPanel, tile_cols) * (fmt == BT_BFP8 ? 8 : 4);
+  const dim3 grid((unsigned)((units + 255) / 256), (unsigned)runs);
+  if (fmt == BT_BFP8 && to_stream) to_stream_kernel<BT_BFP8><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else if (to_stream) to_stream_kernel<BT_BFP4><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else if (fmt == BT_BFP8) from_stream_kernel<BT_BFP8><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  else from_stream_kernel<BT_BFP4><<<grid, 256, 0, st>>>(s8, d8, tile_rows, tile_cols);
+  return launched(to_stream ? "to_stream_kernel" : "from_stream_kernel");
 }
 
 }  // extern "C"

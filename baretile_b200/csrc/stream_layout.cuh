@@ -91,6 +91,25 @@ __host__ __device__ inline uint32_t stream_code_word(uint32_t w) {
   return ((q | 0x88888888u) & ~neg) | ((0x88888888u - q) & 0x77777777u & neg);
 }
 
+// And back, streamed -> canonical, four value bytes at once. Per byte (per nibble): offset + q becomes q, offset - q
+// becomes sign | q (0x80 - u without its top bit, then the sign), and 0 becomes "minus zero", the sign alone, which
+// the same expression gives (0x80 - 0 without its top bit is 0).
+template <int FMT>
+__host__ __device__ inline uint32_t canonical_code_word(uint32_t u) {
+  if (FMT == BT_BFP8) {
+    const uint32_t q = u & 0x7F7F7F7Fu;
+    uint32_t pos;                                   // all ones in the bytes that hold a positive code (top bit set)
+#ifdef __CUDA_ARCH__
+    asm("prmt.b32 %0, %1, 0, 0xBA98;" : "=r"(pos) : "r"(u));
+#else
+    pos = (u >> 7 & 0x01010101u) * 0xFFu;
+#endif
+    return (q & pos) | ((((0x80808080u - q) & 0x7F7F7F7Fu) | 0x80808080u) & ~pos);
+  }
+  const uint32_t q = u & 0x77777777u, pos = (u >> 3 & 0x11111111u) * 0xFu;
+  return (q & pos) | ((((0x88888888u - q) & 0x77777777u) | 0x88888888u) & ~pos);
+}
+
 #ifdef __CUDACC__
 // bf16 lanes 2^(e - 64) for two exponent bytes of a lane's exponent word `ew`: bytes 0 and 2 (HI = 0, the lane's
 // first k pair) or bytes 1 and 3 (HI = 1, its second pair). e << 7 is the exponent field, 0x1F80 = 63 << 7 the bias

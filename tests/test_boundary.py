@@ -205,6 +205,9 @@ def test_newer_entry_points_refuse_bad_arguments_before_any_device_work(built):
   # put: formats, distinct aligned tensors
   with pytest.raises(ValueError, match="unknown format"): _lib.call("bt_put", 0, 3, 256, 512, 768, 1, 1, 32, 32, 0, 0)
   with pytest.raises(ValueError, match="apart from dst"): _lib.call("bt_put", 0, 8, 256, 256, 768, 1, 1, 32, 32, 0, 0)
+  # the streaming layout: one launch takes up to 65535 runs of 4 tile columns; and an event to wait for must exist
+  with pytest.raises(ValueError, match="tile columns in one launch"): _lib.call("bt_relayout", 0, 8, 1, 1, 4 * 65535 + 1, 256, 512, 0)
+  with pytest.raises(ValueError, match="null event"): _lib.call("bt_stream_wait_event", 0, 0, 0)
   # many small matrices: a table is needed
   with pytest.raises(ValueError, match="no matrices"): _lib.call("bt_tilize_many", 0, 2, 0, None, None, None, None, 0)
   with pytest.raises(ValueError, match="itemsize"): _lib.call("bt_untilize_many", 0, 3, 1, None, None, None, None, 0)
