@@ -115,7 +115,8 @@ int bt_put(int device, int fmt, uint64_t dst, uint64_t x, uint64_t ids, int batc
 /* Tensor.columns() / columns_kernel (baretile/tensor.py:598-611, baretile/kernels.py:1455-1481): a pure
  * byte permutation of a (tile_rows x tile_cols) block-float matrix into the layout the matmul streams.
  * Runs of 4 tile columns; inside a run, tile row by tile row; inside a tile, exponents then values,
- * both ordered for one 128-bit load per lane. to_stream = 0 undoes it. */
+ * both ordered for one 128-bit load per lane, value bytes recoded one to one from sign and magnitude to offset
+ * binary. to_stream = 0 undoes it, byte for byte. One launch takes up to 262140 tile columns. */
 int bt_relayout(int device, int fmt, int to_stream, int tile_rows, int tile_cols, uint64_t src, uint64_t dst,
                 uint64_t stream);
 
