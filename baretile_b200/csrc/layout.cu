@@ -129,31 +129,48 @@ __global__ void many_kernel(const ManyArgs a) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= a.first[a.n]) return;
   int k = 0;
-  while (i >= a.first[k + 1]) k++;
+#pragma unroll
+  for (int step = kManyMax / 2; step > 0; step /= 2)                   // the last item whose first half run is not past i
+    if (k + step < a.n && i >= a.first[k + step]) k += step;
   const int rows = a.rows[k], cols = a.cols[k], tc = (cols + 31) / 32, h = i - a.first[k];
   const int tile = h / 128, in = h % 128, face = in / 32, r16 = in % 32 / 2, c8 = in % 2 * 8;
   int r = tile / tc * 32 + face / 2 * 16 + r16;
   const int c0 = tile % tc * 32 + face % 2 * 16 + c8;
+  constexpr int W = (int)sizeof(T) * 8 / 16;                           // 16-byte words of a half run
+  // rows that start on a 16-byte boundary and hold a multiple of 8 datums move as whole 16-byte words
+  const bool wide = cols % 8 == 0 && (reinterpret_cast<uintptr_t>(TILIZE ? a.src[k] : a.dst[k]) & 15) == 0;
   __align__(16) T v[8];
   if (TILIZE) {
     if (rows == 1) r = 0;                                              // a single row fills its tile
     const T *row = static_cast<const T *>(a.src[k]) + (size_t)r * cols;
+    if (wide) {
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-      const int c = cols == 1 ? 0 : c0 + j;                            // a single column repeats
-      v[j] = (r < rows && c < cols) ? row[c] : T(0);
+      for (int j = 0; j < W; j++) reinterpret_cast<uint4 *>(v)[j] = r < rows && c0 < cols ? reinterpret_cast<const uint4 *>(row + c0)[j] : make_uint4(0, 0, 0, 0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int c = cols == 1 ? 0 : c0 + j;                          // a single column repeats
+        v[j] = (r < rows && c < cols) ? row[c] : T(0);
+      }
     }
     uint4 *o = reinterpret_cast<uint4 *>(static_cast<T *>(a.dst[k]) + (size_t)h * 8);
 #pragma unroll
-    for (int j = 0; j < (int)(sizeof(v) / 16); j++) o[j] = reinterpret_cast<const uint4 *>(v)[j];
+    for (int j = 0; j < W; j++) o[j] = reinterpret_cast<const uint4 *>(v)[j];
   } else {
     if (r >= rows) return;
 #pragma unroll
-    for (int j = 0; j < (int)(sizeof(v) / 16); j++) reinterpret_cast<uint4 *>(v)[j] = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.src[k]) + (size_t)h * 8)[j];
+    for (int j = 0; j < W; j++) reinterpret_cast<uint4 *>(v)[j] = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.src[k]) + (size_t)h * 8)[j];
     T *row = static_cast<T *>(a.dst[k]) + (size_t)r * cols;
+    if (wide) {
+      if (c0 < cols) {
 #pragma unroll
-    for (int j = 0; j < 8; j++)
-      if (c0 + j < cols) row[c0 + j] = v[j];
+        for (int j = 0; j < W; j++) reinterpret_cast<uint4 *>(row + c0)[j] = reinterpret_cast<const uint4 *>(v)[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (c0 + j < cols) row[c0 + j] = v[j];
+    }
   }
 }
 
